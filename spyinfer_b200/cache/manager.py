@@ -31,7 +31,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 import numpy as np
 import torch
 
-from ..config.spec import PagedCacheNeed, StateCacheNeed
+from ..config.spec import CompositeCacheNeed, PagedCacheNeed, StateCacheNeed
 from . import core
 from .core import NoFreeSlot, OutOfPages
 
@@ -42,14 +42,22 @@ __all__ = ["CacheManager", "CacheView", "NoFreeSlot", "OutOfPages"]
 class CacheView:
     """What one run-order entry's mixer sees of the cache during a step."""
 
-    kind: str                      # "paged", "state" or "none"
+    kind: str                      # "paged", "state", "composite" or "none"
     group: int = -1
     pages: Optional[torch.Tensor] = None        # [pages, 2, kv_heads, page_size, head_dim] of this entry
     block_table: Optional[torch.Tensor] = None  # [S, width] int32 on the device, set for each step
     page_size: int = 0
     window: Optional[int] = None
     writes: bool = True            # False: the entry reads another entry's cache
-    state: Optional[torch.Tensor] = None        # [slots, *shape] of this entry
+    state: Optional[torch.Tensor] = None        # [slots + 1, *shape] of this entry (the last row is the spare slot)
+    stride: int = 1                # tokens an entry of the pages stands for
+    parts: Optional[List["CacheView"]] = None   # "composite": one view for each part of the need, in its order
+
+    def paged_views(self) -> List["CacheView"]:
+        """This view if it is paged, or the paged ones among a composite's parts."""
+        if self.kind == "paged":
+            return [self]
+        return [v for p in (self.parts or []) for v in p.paged_views()]
 
 
 class _PagedGroup:
@@ -84,43 +92,51 @@ class CacheManager:
         self._views: List[CacheView] = []
         cache_of = list(cache_of) if cache_of is not None else [None] * len(needs)
         by_key: Dict[Hashable, int] = {}
-        self._entry_slot_in_group: List[int] = []
-        for i, need in enumerate(needs):
-            if cache_of[i] is not None:
-                src = self._views[cache_of[i]]
-                self._views.append(CacheView(kind=src.kind, group=src.group, page_size=src.page_size, window=src.window, writes=False))
-                self._entry_slot_in_group.append(self._entry_slot_in_group[cache_of[i]])
-                self.state_tensors.append(None)
-                continue
+        self._paged: List[tuple] = []              # (view, its index among its group's entries) of every paged view that owns pages
+
+        def shared(src: CacheView) -> CacheView:
+            """The view of an entry that reads another entry's cache and stores nothing."""
+            v = CacheView(kind=src.kind, group=src.group, page_size=src.page_size, window=src.window, writes=False, state=src.state, stride=src.stride)
+            if src.parts is not None:
+                v.parts = [shared(p) for p in src.parts]
+            if src.kind == "paged":
+                self._paged.append((v, dict((id(w), k) for w, k in self._paged)[id(src)]))
+            return v
+
+        def make(i: int, need) -> CacheView:
             if need is None:
-                self._views.append(CacheView(kind="none"))
-                self._entry_slot_in_group.append(-1)
-                self.state_tensors.append(None)
-            elif isinstance(need, PagedCacheNeed):
+                return CacheView(kind="none")
+            if isinstance(need, CompositeCacheNeed):
+                return CacheView(kind="composite", parts=[make(i, p) for p in need.parts])
+            if isinstance(need, PagedCacheNeed):
                 key = need.group_key()
                 if key not in by_key:
                     by_key[key] = len(self.groups)
                     self.groups.append(_PagedGroup(need))
                 g = by_key[key]
-                self._entry_slot_in_group.append(len(self.groups[g].entries))
+                v = CacheView(kind="paged", group=g, page_size=page_size, window=need.window, stride=need.stride)
+                self._paged.append((v, len(self.groups[g].entries)))
                 self.groups[g].entries.append(i)
-                self._views.append(CacheView(kind="paged", group=g, page_size=page_size, window=need.window))
-                self.state_tensors.append(None)
-            elif isinstance(need, StateCacheNeed):
+                return v
+            if isinstance(need, StateCacheNeed):
                 t = None
                 if device is not None:
-                    t = torch.zeros((max_num_seqs,) + tuple(need.shape), dtype=getattr(torch, need.dtype), device=device)
-                self._views.append(CacheView(kind="state", state=t))
-                self._entry_slot_in_group.append(-1)
+                    # one row more than there are slots: the spare slot (the last row) takes the state of the padding
+                    # rows of a fixed-size (captured) batch
+                    t = torch.zeros((max_num_seqs + 1,) + tuple(need.shape), dtype=getattr(torch, need.dtype), device=device)
                 self.state_tensors.append(t)
-            else:
-                raise TypeError(f"run-order entry {i}: unknown cache need {need!r}")
+                return CacheView(kind="state", state=t)
+            raise TypeError(f"run-order entry {i}: unknown cache need {need!r}")
+
+        for i, need in enumerate(needs):
+            self._views.append(shared(self._views[cache_of[i]]) if cache_of[i] is not None else make(i, need))
         # the bookkeeping (pools, block tables, slots, requests) lives in the C++ engine core
         self._lib = core.lib()
         windows = (ctypes.c_int * max(1, len(self.groups)))(*[(-1 if g.need.window is None else int(g.need.window)) for g in self.groups])
-        self.group_pages = [self.pages_of_group(g.need.window, page_size, num_pages, max_num_seqs, max_step_tokens) for g in self.groups]
+        self.group_pages = [self.pages_of_group(g.need.window, page_size, num_pages, max_num_seqs, max_step_tokens, g.need.stride) for g in self.groups]
         sizes = (ctypes.c_int * max(1, len(self.groups)))(*self.group_pages)
-        self._h = self._lib.spy_cache_create(len(self.groups), windows, sizes, page_size, num_pages, max_num_seqs, max_model_len)
+        strides = (ctypes.c_int * max(1, len(self.groups)))(*[int(g.need.stride) for g in self.groups])
+        self._h = self._lib.spy_cache_create(len(self.groups), windows, sizes, strides, page_size, num_pages, max_num_seqs, max_model_len)
         if not self._h:
             raise ValueError(core.build.last_error("engine_core"))
         for gi, g in enumerate(self.groups):
@@ -131,11 +147,9 @@ class CacheManager:
                 # one page more than the pool hands out: the spare page (the id after the pool's last) takes
                 # the writes of the padding rows of a fixed-size (captured) decode batch
                 g.pages = torch.zeros((len(g.entries), pool_pages + 1, 2, n.num_kv_heads, page_size, n.head_dim), dtype=dtype, device=device)
-        for i, v in enumerate(self._views):
-            if v.kind == "paged" and self.groups[v.group].pages is not None:
-                v.pages = self.groups[v.group].pages[self._entry_slot_in_group[i]]
-            if v.kind == "state" and not v.writes and cache_of[i] is not None:
-                v.state = self._views[cache_of[i]].state
+        for v, k in self._paged:
+            if self.groups[v.group].pages is not None:
+                v.pages = self.groups[v.group].pages[k]
         self._handles: Dict[Hashable, int] = {}    # request ids that are no small integers -> handles of the core
         self._names: Dict[int, Hashable] = {}
 
@@ -166,8 +180,12 @@ class CacheManager:
 
     # ---- sizes -------------------------------------------------------------------------
     @staticmethod
-    def pages_of_group(window: Optional[int], page_size: int, num_pages: int, max_num_seqs: int, max_step_tokens: Optional[int]) -> int:
-        """The pool size of a group with this window (None: every key is kept)."""
+    def pages_of_group(window: Optional[int], page_size: int, num_pages: int, max_num_seqs: int, max_step_tokens: Optional[int], stride: int = 1) -> int:
+        """The pool size of a group with this window (None: every key is kept) and stride (an entry for
+        every so many tokens: the requests of a full pool of ``num_pages`` then hold a ``stride``-th of
+        that many entries, and each of them may leave one page partly filled)."""
+        if stride > 1:
+            return max(1, min(num_pages, (num_pages + stride - 1) // stride + max_num_seqs))
         if window is None or max_step_tokens is None:
             return num_pages
         per_request = (int(window) + int(max_step_tokens) + page_size - 1) // page_size + 2
@@ -178,14 +196,15 @@ class CacheManager:
         """Device bytes that one more page costs in every group that keeps every key (windowed
         groups are bounded by their window, see ``pages_of_group``; with only such groups, in every group)."""
         elt = torch.empty((), dtype=dtype).element_size()
-        paged = [n for n in needs if isinstance(n, PagedCacheNeed)]
+        flat = [m for n in needs for m in (n.flat() if isinstance(n, CompositeCacheNeed) else [n])]
+        paged = [n for n in flat if isinstance(n, PagedCacheNeed)]
         full = [n for n in paged if n.window is None] or paged
-        return sum(2 * n.num_kv_heads * page_size * n.head_dim * elt for n in full)
+        return sum(-(-2 * n.num_kv_heads * page_size * n.head_dim * elt // n.stride) for n in full)
 
     def most_tokens_alone(self) -> int:
         """The most tokens of ONE request that the pools can hold (beyond ``max_model_len`` if only
         windowed groups exist: their pages come back as the window passes)."""
-        full = [p for g, p in zip(self.groups, self.group_pages) if g.need.window is None]
+        full = [p * g.need.stride for g, p in zip(self.groups, self.group_pages) if g.need.window is None]
         return min(full) * self.page_size if full else max(self.max_model_len, self.num_pages * self.page_size)
 
     def pages_for(self, length: int) -> int:
@@ -277,6 +296,11 @@ class CacheManager:
         if rc == 5:
             raise KeyError(rid)
         core.check(rc)
+
+    @property
+    def spare_slot(self) -> int:
+        """The row of every state tensor that no request ever holds (the padding of fixed-size batches uses it)."""
+        return self.max_num_seqs
 
     def spare_page(self, group: int = 0) -> int:
         """Id of the page of ``group`` that no request ever holds (see the pages tensor's allocation)."""

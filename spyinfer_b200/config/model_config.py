@@ -39,6 +39,11 @@ class ArchitectureConfig:
     def to_spec(self) -> ModelSpec:
         raise NotImplementedError
 
+    def sizes_from_tensors(self, shape_of) -> None:
+        """Called after ``from_json`` when the configuration is read from a model folder: an architecture whose
+        config.json leaves a size to the tensors' shapes takes it from ``shape_of(tensor name)`` (a tuple, or None when
+        the checkpoint has no such tensor).  The default needs nothing."""
+
 
 def register_architecture(name: str, model_type: str = None):
     """Class decorator: ``@register_architecture("Qwen3ForCausalLM", model_type="qwen3")``."""
@@ -58,7 +63,7 @@ def known_architectures():
 
 
 def config_from_json(data: Dict[str, Any]) -> ArchitectureConfig:
-    archs = data.get("architectures")
+    archs = data.get("architectures", data.get("architecture"))     # a list, or one name under either key
     if isinstance(archs, str):
         archs = [archs]
     if not archs or not isinstance(archs, list):
@@ -82,4 +87,21 @@ def load_model_config(model_dir: str) -> ArchitectureConfig:
             data = json.load(f)
         except json.JSONDecodeError as e:
             raise ConfigError(f"{path}: not valid JSON ({e})") from None
-    return config_from_json(data)
+    config = config_from_json(data)
+    if type(config).sizes_from_tensors is not ArchitectureConfig.sizes_from_tensors:
+        from ..weights.safetensors_io import SafetensorsError, SafetensorsFile, shard_paths
+        try:
+            files = [SafetensorsFile(p) for p in shard_paths(model_dir)]
+        except SafetensorsError:
+            files = []                      # a folder without weights: the sizes must all be in config.json
+        try:
+            def shape_of(name):
+                for f in files:
+                    if name in f.entries:
+                        return tuple(f.shape(name))
+                return None
+            config.sizes_from_tensors(shape_of)
+        finally:
+            for f in files:
+                f.close()
+    return config

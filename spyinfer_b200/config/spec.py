@@ -43,6 +43,7 @@ class LayerSpec:
     feed_forward: Optional[PartSpec] = None
     weight_prefix: str = ""
     more: Dict[str, PartSpec] = field(default_factory=dict)
+    block_params: Dict[str, Any] = field(default_factory=dict)     # the arrangement's own constants
 
     def roles(self) -> Dict[str, PartSpec]:
         """role -> part, in the order the parts' tensors are declared."""
@@ -54,7 +55,7 @@ class LayerSpec:
         return out
 
     def __hash__(self):
-        return hash((self.block, self.weight_prefix, tuple(self.roles().items())))
+        return hash((self.block, self.weight_prefix, tuple(self.roles().items()), repr(sorted(self.block_params.items()))))
 
 
 @dataclass(frozen=True)
@@ -83,6 +84,7 @@ class ModelSpec:
     max_position: int
     eos_token_id: int = -1
     bos_token_id: int = -1
+    ignorable: List[str] = field(default_factory=list)     # tensors a checkpoint may hold without the model using them
 
     def validate(self) -> None:
         if not self.layers:
@@ -102,16 +104,24 @@ class PagedCacheNeed:
     """A mixer that keeps keys and values of past tokens in pages.
 
     ``window`` is ``None`` when every past key is kept, else the number of most recent
-    keys (the query's own included) that a query can see.  Entries of the run order with
-    equal needs share one group of pages in the cache manager.
+    positions (the query's own included) whose entries the mixer still reads; older pages are
+    given back.  ``stride`` above 1: the mixer keeps one entry for every ``stride`` tokens (a
+    summary of each block of that many tokens, stored when the block's last token is), so a
+    request of ``L`` tokens holds ``L // stride`` entries; such a need has no window.  Entries of
+    the run order with equal needs share one group of pages in the cache manager.
     """
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    stride: int = 1
+
+    def __post_init__(self):
+        if self.stride < 1 or (self.stride > 1 and self.window is not None):
+            raise ValueError(f"a paged need's stride must be at least 1, and with a stride above 1 there is no window (found stride {self.stride}, window {self.window})")
 
     def group_key(self) -> Tuple:
-        return ("paged", self.num_kv_heads, self.head_dim, self.window)
+        return ("paged", self.num_kv_heads, self.head_dim, self.window, self.stride)
 
 
 @dataclass(frozen=True)
@@ -123,3 +133,17 @@ class StateCacheNeed:
 
     def group_key(self) -> Tuple:
         return ("state", tuple(self.shape), self.dtype)
+
+
+@dataclass(frozen=True)
+class CompositeCacheNeed:
+    """A mixer that keeps several things: each part is a ``PagedCacheNeed`` or a ``StateCacheNeed``
+    (or None), and the mixer's ``CacheView`` holds one view for each in ``parts``, in this order."""
+
+    parts: Tuple
+
+    def flat(self):
+        out = []
+        for p in self.parts:
+            out += p.flat() if isinstance(p, CompositeCacheNeed) else [p]
+        return out

@@ -1,0 +1,212 @@
+// Attention over a window of recent keys plus one pooled key and value for every block of tokens that
+// lies wholly before the window, all under one softmax; and the kernel that makes the pooled entries.
+//
+// A query at position p of sequence s sees
+//   * the keys j with p - window < j <= p, from the token cache (page block_table[s, j / page_size], slot j % page_size);
+//   * the pooled entries b with b * pool + pool - 1 <= p - window, from the pooled cache (one entry for every `pool`
+//     tokens: page pool_table[s, b / page_size], slot b % page_size), entry b being the mean of the keys (values) of the
+//     positions b * pool .. b * pool + pool - 1 as the token cache holds them.
+// A token that has left the window while its block is not yet complete enough to be seen is seen by nobody.
+// kv head = head / (nh / nkv); score = (q . k) * scale; p = exp(score - max) / sum; o = sum p v.
+//
+// This is the plain kernel (one block per (query token, head), everything in 32-bit, any head size that is a multiple
+// of 4, any page size, 32-bit or bfloat16 storage); it serves prompt portions and decoding alike.  The keys of a query
+// form one list, pooled entries first, and are processed in chunks of 128 of that list, so a query's result does not
+// depend on how the batch was cut.
+#include "common.cuh"
+
+SPY_MODULE(spy_attention_pool)
+
+constexpr int CHUNK = 128;
+
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4])
+    {
+        const float4 x = *reinterpret_cast<const float4*>(p);
+        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+    }
+};
+template <> struct Vec4<bf16> {
+    static __device__ __forceinline__ void load(const bf16* p, float (&v)[4])
+    {
+        const uint2 x = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&x.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&x.y);
+        v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+    }
+};
+
+// ---- pooled entries ------------------------------------------------------------------------------
+// One block per (token, K or V, kv head); a token whose position ends a block of `pool` tokens writes that block's entry.
+template <typename TC>
+__global__ void pool_store_kernel(const TC* __restrict__ pages, int num_pages, const int* __restrict__ block_table, TC* __restrict__ pooled,
+                                  int num_pooled_pages, const int* __restrict__ pool_table, int table_width, int page_size, int nkv, int hd, int pool,
+                                  const int* __restrict__ positions, const int* __restrict__ seq_of_token, int* status)
+{
+    pdl_enter();
+    const int t = blockIdx.x, which = blockIdx.y / nkv, kvh = blockIdx.y % nkv;
+    const int pos = positions[t];
+    if ((pos + 1) % pool != 0) return;
+    const int b = (pos + 1) / pool - 1, seq = seq_of_token[t];
+    const int* bt = block_table + (size_t)seq * table_width;
+    const int lp_out = b / page_size;
+    const int out_page = lp_out < table_width ? pool_table[(size_t)seq * table_width + lp_out] : -1;
+    if (out_page < 0 || out_page >= num_pooled_pages) {
+        if (threadIdx.x == 0) report_status(status, SPY_STATUS_BAD_PAGE, t);
+        return;
+    }
+    TC* dst = pooled + ((((size_t)out_page * 2 + which) * nkv + kvh) * page_size + b % page_size) * hd;
+    const float inv = 1.0f / (float)pool;
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float sum = 0.f;
+        for (int j = b * pool; j <= pos; ++j) {
+            const int lp = j / page_size;
+            const int page = lp < table_width ? bt[lp] : -1;
+            if (page < 0 || page >= num_pages) {
+                report_status(status, SPY_STATUS_BAD_PAGE, t);
+                continue;
+            }
+            sum += to_f32(pages[((((size_t)page * 2 + which) * nkv + kvh) * page_size + j % page_size) * hd + d]);
+        }
+        dst[d] = from_f32<TC>(sum * inv);
+    }
+}
+
+extern "C" int spy_pool_store(const void* pages, int num_pages, const int* block_table, void* pooled, int num_pooled_pages, const int* pool_table,
+                              int table_width, int page_size, int nkv, int hd, int cache_dtype, int pool, const int* positions, const int* seq_of_token,
+                              int tokens, int* status, cudaStream_t stream)
+{
+    if (tokens <= 0) return 0;
+    if (pool <= 0 || page_size <= 0 || nkv <= 0 || hd <= 0 || table_width <= 0) SPY_FAIL("pool_store: pool, page_size, heads, head size and table width must be positive");
+    if (2 * nkv > 65535) SPY_FAIL("pool_store: %d key/value heads exceed the grid limit", nkv);
+    int threads = (hd + 31) / 32 * 32;
+    if (threads > 256) threads = 256;
+    SPY_DISPATCH_DTYPE(cache_dtype, TC, {
+        spy_launch(pool_store_kernel<TC>, dim3(tokens, 2 * nkv), dim3(threads), 0, stream, (const TC*)pages, num_pages, block_table, (TC*)pooled,
+                   num_pooled_pages, pool_table, table_width, page_size, nkv, hd, pool, positions, seq_of_token, status);
+    })
+    SPY_CHECK_LAUNCH("pool_store");
+    return 0;
+}
+
+// ---- attention -------------------------------------------------------------------------------------
+template <typename TA, typename TC>
+__global__ void __launch_bounds__(CHUNK)
+attention_pool_kernel(const TA* __restrict__ q, long long q_row_stride, TA* __restrict__ out, const TC* __restrict__ pages, int num_pages,
+                      const int* __restrict__ block_table, const TC* __restrict__ pooled, int num_pooled_pages, const int* __restrict__ pool_table,
+                      int table_width, int page_size, int nh, int nkv, int hd, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                      int window, int pool, float scale, int* status)
+{
+    extern __shared__ float smem[];
+    pdl_enter();
+    float* q_s = smem;                                   // hd
+    float* p_s = q_s + hd;                               // CHUNK
+    const TC** row_s = (const TC**)(p_s + CHUNK);        // CHUNK pointers to K rows; 8-byte aligned: hd % 4 == 0, CHUNK even
+    float* scratch = (float*)(row_s + CHUNK);            // 33
+
+    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int pos = positions[t];
+    const int seq = seq_of_token[t];
+    const int kvh = h / (nh / nkv);
+    const int* bt = block_table + (size_t)seq * table_width;
+    const int* pt = pool_table ? pool_table + (size_t)seq * table_width : nullptr;
+    const long long v_offset = (long long)nkv * page_size * hd;  // from a K row to its V row, in both caches
+
+    const TA* q_row = q + (size_t)t * q_row_stride + (size_t)h * hd;
+    for (int d = tid; d < hd; d += CHUNK) q_s[d] = to_f32(q_row[d]);
+
+    const int lo = max(0, pos - window + 1);
+    const int nb = (pool > 0 && pos - window + 1 >= pool) ? (pos - window + 1) / pool : 0;   // blocks that end at or before pos - window
+    const int total = nb + (pos - lo + 1);
+    float m = -INFINITY, l = 0.f;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};  // dims tid, tid+128, tid+256, tid+384
+    __syncthreads();
+
+    for (int c0 = 0; c0 < total; c0 += CHUNK) {
+        const int idx = c0 + tid;
+        bool valid = idx < total;
+        const TC* row = nullptr;
+        if (valid) {
+            const bool is_pooled = idx < nb;
+            const int e = is_pooled ? idx : lo + (idx - nb);     // entry of the pooled cache, or position in the token cache
+            const int lp = e / page_size;
+            const int page = lp < table_width ? (is_pooled ? pt[lp] : bt[lp]) : -1;
+            if (page < 0 || page >= (is_pooled ? num_pooled_pages : num_pages)) {
+                report_status(status, SPY_STATUS_BAD_PAGE, t);
+                valid = false;
+            } else {
+                row = (is_pooled ? pooled : pages) + ((((long long)page * 2) * nkv + kvh) * page_size + e % page_size) * hd;
+            }
+        }
+        float s = -INFINITY;
+        if (valid) {
+            float dot = 0.f;
+            for (int d = 0; d < hd; d += 4) {
+                float kv[4];
+                Vec4<TC>::load(row + d, kv);
+                dot = fmaf(q_s[d], kv[0], dot);
+                dot = fmaf(q_s[d + 1], kv[1], dot);
+                dot = fmaf(q_s[d + 2], kv[2], dot);
+                dot = fmaf(q_s[d + 3], kv[3], dot);
+            }
+            s = dot * scale;
+        }
+        const float chunk_max = block_max(s, scratch);
+        const float m_new = fmaxf(m, chunk_max);
+        if (m_new == -INFINITY) continue;  // every key of the chunk was refused: nothing to add (uniform over the block)
+        const float p = valid ? expf(s - m_new) : 0.f;
+        const float alpha = m == -INFINITY ? 0.f : expf(m - m_new);
+        p_s[tid] = p;
+        row_s[tid] = row;
+        const float chunk_sum = block_sum(p, scratch);  // its barriers also publish p_s and row_s
+        l = l * alpha + chunk_sum;
+        m = m_new;
+        const int count = min(CHUNK, total - c0);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int d = tid + r * CHUNK;
+            if (d < hd) {
+                float a = acc[r] * alpha;
+                for (int jj = 0; jj < count; ++jj)
+                    if (row_s[jj] != nullptr) a = fmaf(p_s[jj], to_f32(row_s[jj][v_offset + d]), a);
+                acc[r] = a;
+            }
+        }
+        __syncthreads();  // p_s and row_s are rewritten by the next chunk
+    }
+    TA* o_row = out + ((size_t)t * nh + h) * hd;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int d = tid + r * CHUNK;
+        if (d < hd) o_row[d] = from_f32<TA>(l > 0.f ? acc[r] / l : 0.f);
+    }
+}
+
+// q: [T, ...] rows of q_row_stride elements whose first nh*hd elements are the query heads; out: [T, nh*hd];
+// pages / pooled: caches [pages][2][nkv][page_size][hd] of cache_dtype with a block table [S, table_width] each
+// (pool == 0: no pooled entries, pooled and pool_table may be null).
+extern "C" int spy_attention_pool(const void* q, long long q_row_stride, void* out, int act_dtype, const void* pages, int num_pages,
+                                  const int* block_table, const void* pooled, int num_pooled_pages, const int* pool_table, int cache_dtype,
+                                  int table_width, int page_size, int nh, int nkv, int hd, const int* positions, const int* seq_of_token, int tokens,
+                                  int window, int pool, float scale, int* status, cudaStream_t stream)
+{
+    if (tokens <= 0) return 0;
+    if (nh <= 0 || nkv <= 0 || nh % nkv != 0) SPY_FAIL("attention: %d query heads do not group over %d key/value heads", nh, nkv);
+    if (hd <= 0 || hd % 4 != 0 || hd > 4 * CHUNK) SPY_FAIL("attention: head_dim %d must be a multiple of 4, at most %d", hd, 4 * CHUNK);
+    if (page_size <= 0 || num_pages <= 0 || table_width <= 0) SPY_FAIL("attention: page_size, num_pages and table_width must be positive");
+    if (window <= 0) SPY_FAIL("attention: window %d must be positive", window);
+    if (pool < 0 || (pool > 0 && (pooled == nullptr || pool_table == nullptr || num_pooled_pages <= 0))) SPY_FAIL("attention: pooled entries need their cache and block table");
+    if (nh > 65535) SPY_FAIL("attention: %d heads exceed the grid limit", nh);
+    const size_t smem = (size_t)(hd + CHUNK + 33) * sizeof(float) + (size_t)CHUNK * sizeof(void*);
+    dim3 grid(tokens, nh);
+    SPY_DISPATCH_DTYPE(act_dtype, TA, {
+        SPY_DISPATCH_DTYPE(cache_dtype, TC, {
+            spy_launch(attention_pool_kernel<TA, TC>, grid, dim3(CHUNK), smem, stream, (const TA*)q, q_row_stride, (TA*)out, (const TC*)pages, num_pages,
+                       block_table, (const TC*)pooled, num_pooled_pages, pool_table, table_width, page_size, nh, nkv, hd, positions, seq_of_token, window,
+                       pool, scale, status);
+        })
+    })
+    SPY_CHECK_LAUNCH("attention_pool");
+    return 0;
+}

@@ -66,9 +66,12 @@ struct PagePool {
 
 struct Group {
     int window;                    // -1: every key is kept
+    int stride;                    // one entry of the group for every `stride` tokens of a request (1: an entry a token);
+                                   // an entry exists once all its tokens do, so a request of L tokens holds L / stride entries
     PagePool pool;
     std::vector<int32_t> tables;   // [max_num_seqs][width], row = state slot, -1 = no page
-    Group(int window_, int num_pages, int max_num_seqs, int width) : window(window_), pool(num_pages), tables((size_t)max_num_seqs * width, -1) {}
+    Group(int window_, int stride_, int num_pages, int max_num_seqs, int width)
+        : window(window_), stride(stride_), pool(num_pages), tables((size_t)max_num_seqs * width, -1) {}
 };
 
 struct Request {
@@ -95,25 +98,43 @@ struct Cache {
         auto it = requests.find(rid);
         return it == requests.end() ? nullptr : &it->second;
     }
-    int pages_needed(const Request& r, int new_length) const { return std::max(0, pages_for(new_length) - pages_for(r.reserved)); }
+    // pages of group g that hold the entries of a request of `length` tokens
+    int pages_for(const Group& g, int length) const { return (length / g.stride + page_size - 1) / page_size; }
+    int pages_needed(const Group& g, const Request& r, int new_length) const { return std::max(0, pages_for(g, new_length) - pages_for(g, r.reserved)); }
+    // the most over the groups (a model without paged groups needs none)
+    int pages_needed(const Request& r, int new_length) const
+    {
+        if (groups.empty()) return std::max(0, pages_for(new_length) - pages_for(r.reserved));
+        int most = 0;
+        for (const Group& g : groups) most = std::max(most, pages_needed(g, r, new_length));
+        return most;
+    }
     bool can_reserve(const Request& r, int new_length) const
     {
         if (new_length > max_model_len) return false;
-        const int need = pages_needed(r, new_length);
         for (const Group& g : groups)
-            if (g.pool.num_free() < need) return false;
+            if (g.pool.num_free() < pages_needed(g, r, new_length)) return false;
         return true;
+    }
+    // The longest a request that has `done` tokens (and pages for r.reserved) can become with the pages that are free now.
+    int fit_length(const Request& r) const
+    {
+        long long fit = max_model_len;
+        for (const Group& g : groups) {
+            const long long entries = (long long)(pages_for(g, r.reserved) + g.pool.num_free()) * page_size;
+            fit = std::min(fit, entries * g.stride + (g.stride - 1));
+        }
+        return (int)fit;
     }
     // All or nothing: no page is taken when one group cannot give what is needed.
     int reserve(int64_t rid, Request& r, int new_length)
     {
         if (new_length > max_model_len) return fail(BAD_VALUE, "request %lld: %d tokens exceed max_model_len %d", (long long)rid, new_length, max_model_len);
         if (new_length <= r.reserved) return OK;
-        const int need = pages_needed(r, new_length);
         for (const Group& g : groups)
-            if (g.pool.num_free() < need) return fail(OUT_OF_PAGES, "Out of memory: No free blocks available.");
-        const int first = pages_for(r.reserved), last = pages_for(new_length);
+            if (g.pool.num_free() < pages_needed(g, r, new_length)) return fail(OUT_OF_PAGES, "Out of memory: No free blocks available.");
         for (Group& g : groups) {
+            const int first = pages_for(g, r.reserved), last = pages_for(g, new_length);
             int32_t* row = g.tables.data() + (size_t)r.slot * width;
             for (int lp = first; lp < last; ++lp) row[lp] = g.pool.allocate();
         }
@@ -184,9 +205,16 @@ int spy_pool_free(void* h, int page) { return static_cast<PagePool*>(h)->release
 // windows[g]: the window of group g in tokens, or -1.  group_pages[g]: the pages of group g's pool
 // (null: num_pages for every group); a windowed group, whose requests give pages back as the window
 // passes them, can do with fewer than a group that keeps every key.  num_pages is the size of the
-// largest pool.
-void* spy_cache_create(int num_groups, const int* windows, const int* group_pages, int page_size, int num_pages, int max_num_seqs, int max_model_len)
+// largest pool.  strides[g] (null: 1 for every group): group g holds one entry for every strides[g]
+// tokens of a request; such a group has no window.
+void* spy_cache_create(int num_groups, const int* windows, const int* group_pages, const int* strides, int page_size, int num_pages, int max_num_seqs,
+                       int max_model_len)
 {
+    for (int g = 0; strides != nullptr && g < num_groups; ++g)
+        if (strides[g] <= 0 || (strides[g] > 1 && windows[g] >= 0)) {
+            fail(BAD_VALUE, "group %d: stride %d must be positive, and a group with a stride above 1 has no window", g, strides[g]);
+            return nullptr;
+        }
     for (int g = 0; group_pages != nullptr && g < num_groups; ++g)
         if (group_pages[g] <= 0 || group_pages[g] > num_pages) {
             fail(BAD_VALUE, "group %d: %d pages, expected 1..%d", g, group_pages[g], num_pages);
@@ -202,7 +230,7 @@ void* spy_cache_create(int num_groups, const int* windows, const int* group_page
     c->max_num_seqs = max_num_seqs;
     c->max_model_len = max_model_len;
     c->width = (max_model_len + page_size - 1) / page_size;
-    for (int g = 0; g < num_groups; ++g) c->groups.emplace_back(windows[g], group_pages ? group_pages[g] : num_pages, max_num_seqs, c->width);
+    for (int g = 0; g < num_groups; ++g) c->groups.emplace_back(windows[g], strides ? strides[g] : 1, group_pages ? group_pages[g] : num_pages, max_num_seqs, c->width);
     for (int s = max_num_seqs - 1; s >= 0; --s) c->free_slots.push_back(s);   // slot 0 is handed out first
     return c;
 }
@@ -380,7 +408,7 @@ int spy_cache_fill_batch(void* h, int n, const int64_t* rids, const int32_t* cou
     int T = 0, R = 0, longest = 0;
     {   // the checks, before anything is taken
         std::unordered_set<int64_t> seen;
-        long long pages = 0;
+        std::vector<long long> pages(c->groups.size(), 0);
         int slots = 0, t0 = 0;
         for (int i = 0; i < n; ++i) {
             if (!seen.insert(rids[i]).second) return fail(BAD_VALUE, "entry %d: its request appears twice in one step", i);
@@ -392,7 +420,7 @@ int spy_cache_fill_batch(void* h, int n, const int64_t* rids, const int32_t* cou
             const Request& q = r ? *r : fresh;
             if (q.length + cnt > c->max_model_len)
                 return fail(BAD_VALUE, "entry %d: request %lld: %d tokens exceed max_model_len %d", i, (long long)rids[i], q.length + cnt, c->max_model_len);
-            pages += c->pages_needed(q, q.length + cnt);
+            for (size_t g = 0; g < c->groups.size(); ++g) pages[g] += c->pages_needed(c->groups[g], q, q.length + cnt);
             for (int k = 0; k < cnt; ++k) {
                 const int t = tokens[t0 + k];
                 if (t < 0 || t >= vocab_size) return fail(BAD_VALUE, "entry %d: token id %d is outside the vocabulary of %d", i, t, vocab_size);
@@ -402,8 +430,8 @@ int spy_cache_fill_batch(void* h, int n, const int64_t* rids, const int32_t* cou
             t0 += cnt;
         }
         if (slots > (int)c->free_slots.size()) return fail(NO_SLOT, "the step brings %d new requests, %d of %d request slots are free", slots, (int)c->free_slots.size(), c->max_num_seqs);
-        for (const Group& g : c->groups)
-            if (g.pool.num_free() < pages) return fail(OUT_OF_PAGES, "Out of memory: No free blocks available.");
+        for (size_t g = 0; g < c->groups.size(); ++g)
+            if (c->groups[g].pool.num_free() < pages[g]) return fail(OUT_OF_PAGES, "Out of memory: No free blocks available.");
     }
     q_start[0] = 0;
     for (int i = 0; i < n; ++i) {
@@ -514,7 +542,7 @@ int spy_sched_step(void* h, int budget, int chunk, int max_num_seqs, int n_run, 
             if (rest <= 1 || budget <= 0) continue;
             Request* r = c->find(s.id);
             if (!r) return fail(UNKNOWN_REQUEST, "running request %lld holds nothing in the cache", (long long)s.id);
-            const int fit = (c->pages_for(s.done) + c->min_free_pages()) * c->page_size - s.done;
+            const int fit = c->fit_length(*r) - s.done;
             const int n = std::min(std::min(rest, chunk), std::min(budget, fit));
             if (n <= 0) continue;
             if (int rc = c->reserve(s.id, *r, s.done + n)) return rc;
@@ -525,8 +553,9 @@ int spy_sched_step(void* h, int budget, int chunk, int max_num_seqs, int n_run, 
         while (!waiting.empty() && budget > 0 && (int)running.size() < max_num_seqs && !c->free_slots.empty()) {
             Seq s = waiting.front();
             int n = std::min(std::min(s.len - s.done, chunk), budget);
-            if (c->pages_for(n) > c->min_free_pages()) {
-                const int fit = c->min_free_pages() * c->page_size;
+            const Request fresh{-1, 0, 0};
+            if (!c->can_reserve(fresh, n)) {
+                const int fit = c->fit_length(fresh);
                 if (!running.empty() || fit <= 0) break;   // wait for running requests to finish and free pages
                 n = std::min(n, fit);                      // nothing else is running: start with what fits
             }

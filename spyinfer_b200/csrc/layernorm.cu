@@ -1,0 +1,117 @@
+// Layer norm with a weight and no bias, optionally fused with a scaled residual sum and a row gather.
+//   v      = x[row] + scale_a * sum_s a[s][row] + scale_b * sum_s b[s][row]          32-bit sums, parts in their order
+//   x[row] = v                                             when write_back (the residual stream)
+//   out    = (v - mean(v)) / sqrt(mean((v - mean(v))^2) + eps) * w                   32-bit statistics, two passes
+// a and b are null, one array [*, len], or stacks of split-K partial products (splits arrays, split_stride elements
+// apart); two of them because a layer whose mixer is two mixers side by side hands over two results with a weight each.
+// With center == 0 the mean is not removed (an RMS norm with the same fused sums).
+#include "common.cuh"
+
+SPY_MODULE(spy_layernorm)
+
+template <typename TX, typename TD, typename TW, typename TO>
+__global__ void __launch_bounds__(1024)
+layernorm_kernel(TX* x, const TD* __restrict__ a, int a_splits, long long a_stride, float a_scale, const TD* __restrict__ b, int b_splits,
+                 long long b_stride, float b_scale, const int* __restrict__ rows, const TW* __restrict__ w, TO* __restrict__ out, int len, float eps,
+                 int write_back, int center)
+{
+    extern __shared__ float row_buf[];  // len floats, then 33 of scratch
+    pdl_enter();
+    float* scratch = row_buf + len;
+    const int src_row = rows ? rows[blockIdx.x] : blockIdx.x;
+    TX* xr = x + (size_t)src_row * len;
+    const TD* ar = a ? a + (size_t)src_row * len : nullptr;
+    const TD* br = b ? b + (size_t)src_row * len : nullptr;
+    TO* orow = out + (size_t)blockIdx.x * len;
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < len; i += blockDim.x) {
+        float v = to_f32(xr[i]);
+        if (ar) {
+            float d = 0.f;
+            for (int s = 0; s < a_splits; ++s) d += to_f32(ar[(size_t)s * a_stride + i]);
+            v = fmaf(a_scale, d, v);
+        }
+        if (br) {
+            float d = 0.f;
+            for (int s = 0; s < b_splits; ++s) d += to_f32(br[(size_t)s * b_stride + i]);
+            v = fmaf(b_scale, d, v);
+        }
+        row_buf[i] = v;
+        sum += v;
+        if (write_back) xr[i] = from_f32<TX>(v);
+    }
+    const float mean = center ? block_sum(sum, scratch) / (float)len : 0.f;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < len; i += blockDim.x) {
+        const float d = row_buf[i] - mean;
+        ss += d * d;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)len + eps);
+    for (int i = threadIdx.x; i < len; i += blockDim.x) orow[i] = from_f32<TO>(((row_buf[i] - mean) * inv) * to_f32(w[i]));
+}
+
+// x: [*, len] of x_dtype; a, b: null or stacks of delta_dtype; rows: null or n row indices (gather); w: [len] of w_dtype;
+// out: [n, len] of out_dtype.  write_back stores the sum into x and needs rows == null.
+extern "C" int spy_layernorm(void* x, int x_dtype, const void* a, int a_splits, long long a_stride, float a_scale, const void* b, int b_splits,
+                             long long b_stride, float b_scale, int delta_dtype, const int* rows, const void* w, int w_dtype, void* out, int out_dtype,
+                             int n, int len, float eps, int write_back, int center, cudaStream_t stream)
+{
+    if (n <= 0) return 0;
+    if (len <= 0) SPY_FAIL("layernorm: row length %d must be positive", len);
+    if (write_back && rows) SPY_FAIL("layernorm: write_back with a row gather is not defined");
+    if ((a && a_splits <= 0) || (b && b_splits <= 0)) SPY_FAIL("layernorm: a stack of partial sums needs a positive number of parts");
+    if (write_back && !a && !b) write_back = 0;
+    if (!a && !b) delta_dtype = x_dtype;
+    const size_t smem = (size_t)(len + 33) * sizeof(float);
+    if (smem > 227 * 1024) SPY_FAIL("layernorm: a row of %d elements does not fit in shared memory (limit %d)", len, (227 * 1024) / 4 - 33);
+    int threads = (len / 4 + 31) / 32 * 32;
+    threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
+    SPY_DISPATCH_DTYPE(x_dtype, TX, {
+        SPY_DISPATCH_DTYPE(delta_dtype, TD, {
+            SPY_DISPATCH_DTYPE(w_dtype, TW, {
+                SPY_DISPATCH_DTYPE(out_dtype, TO, {
+                    auto kernel = layernorm_kernel<TX, TD, TW, TO>;
+                    if (smem > 48 * 1024) SPY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                    spy_launch(kernel, dim3(n), dim3(threads), smem, stream, (TX*)x, (const TD*)a, a_splits, a_stride, a_scale, (const TD*)b, b_splits,
+                               b_stride, b_scale, rows, (const TW*)w, (TO*)out, len, eps, write_back, center);
+                })
+            })
+        })
+    })
+    SPY_CHECK_LAUNCH("layernorm");
+    return 0;
+}
+
+// out = scale_a * sum_s a[s] + scale_b * sum_s b[s], element by element in 32-bit: the weighted sum of two results (each
+// one array or a stack of partial sums) for a consumer that cannot form it itself.
+template <typename TD>
+__global__ void scaled_sum_kernel(float* __restrict__ out, const TD* __restrict__ a, int a_splits, long long a_stride, float a_scale,
+                                  const TD* __restrict__ b, int b_splits, long long b_stride, float b_scale, long long total)
+{
+    pdl_enter();
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        float x = 0.f, y = 0.f;
+        for (int s = 0; s < a_splits; ++s) x += to_f32(a[(size_t)s * a_stride + i]);
+        for (int s = 0; s < b_splits; ++s) y += to_f32(b[(size_t)s * b_stride + i]);
+        out[i] = fmaf(b_scale, y, a_scale * x);
+    }
+}
+
+extern "C" int spy_scaled_sum(float* out, const void* a, int a_splits, long long a_stride, float a_scale, const void* b, int b_splits, long long b_stride,
+                              float b_scale, int delta_dtype, long long total, cudaStream_t stream)
+{
+    if (total <= 0) return 0;
+    if (!a || !b || a_splits <= 0 || b_splits <= 0) SPY_FAIL("scaled_sum: two results are needed");
+    long long blocks = (total + 255) / 256;
+    const long long most = (long long)spy_sm_count() * 32;
+    if (blocks > most) blocks = most;
+    SPY_DISPATCH_DTYPE(delta_dtype, TD, {
+        spy_launch(scaled_sum_kernel<TD>, dim3((int)blocks), dim3(256), 0, stream, out, (const TD*)a, a_splits, a_stride, a_scale, (const TD*)b, b_splits,
+                   b_stride, b_scale, total);
+    })
+    SPY_CHECK_LAUNCH("scaled_sum");
+    return 0;
+}

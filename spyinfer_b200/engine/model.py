@@ -25,7 +25,7 @@ class _Layer:
     def __init__(self, spec, ctx):
         self.prefix = spec.weight_prefix
         self.by_role = {role: build_part(part, ctx) for role, part in spec.roles().items()}
-        self.block = build_block(spec.block, self.by_role)
+        self.block = build_block(spec.block, self.by_role, spec.block_params)
         self.mixer = self.by_role.get("mixer")          # the part that owns the layer's cache, if the layer has one
         self.feed_forward = self.by_role.get("feed_forward")
 
@@ -58,7 +58,7 @@ class Model:
         return decls
 
     def ignorable_tensors(self) -> List[str]:
-        return list(getattr(self.head, "ignorable", []))
+        return list(getattr(self.head, "ignorable", [])) + list(self.spec.ignorable)
 
     def bind(self, tensors) -> None:
         """``tensors``: every declared tensor by its full name, on the device: a dictionary, or a
@@ -118,20 +118,31 @@ class Model:
     def cache_needs(self):
         """Per run-order entry: its mixer's need, and the entry whose cache it reads instead."""
         needs = [self.layers[e.layer].mixer.cache_need() if self.layers[e.layer].mixer is not None else None for e in self.spec.run_order]
-        return needs, [e.cache_of for e in self.spec.run_order]
+        cache_of = [e.cache_of for e in self.spec.run_order]
+        # what the embedding keeps between steps (a request's last token, if it looks at pairs of tokens) comes after the
+        # run order's entries, as one more entry of the cache manager
+        own = getattr(self.embedding, "cache_need", lambda: None)()
+        return needs + ([own] if own is not None else []), cache_of + ([None] if own is not None else [])
 
     # ---- one step ------------------------------------------------------------------------------
     def forward(self, batch, cache_manager) -> Optional[torch.Tensor]:
-        hidden = self.embedding.forward(batch.token_ids, batch.status)
+        if getattr(self.embedding, "cache_need", lambda: None)() is not None:
+            hidden = self.embedding.forward(batch.token_ids, batch.status, batch=batch, cache=cache_manager.view(len(self.spec.run_order)))
+        else:
+            hidden = self.embedding.forward(batch.token_ids, batch.status)
         delta = None
         for i, entry in enumerate(self.spec.run_order):
             view = cache_manager.view(i)
-            if view.kind == "paged":
-                view.block_table = batch.block_tables[view.group]
+            for paged in view.paged_views():
+                paged.block_table = batch.block_tables[paged.group]
             hidden, delta = self.layers[entry.layer].block.forward(hidden, delta, batch, view)
         if batch.logit_rows.shape[0] == 0:
             return None
-        x = self.final_norm.forward_add(hidden, delta, rows=batch.logit_rows)
+        scale = self.layers[self.spec.run_order[-1].layer].block.residual_scale
+        if scale != 1.0:
+            x = self.final_norm.forward_add(hidden, delta, rows=batch.logit_rows, scale=scale)
+        else:
+            x = self.final_norm.forward_add(hidden, delta, rows=batch.logit_rows)
         return self.head.forward(x)
 
 

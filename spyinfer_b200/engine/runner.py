@@ -90,7 +90,8 @@ class ModelRunner:
     def _pages_from_free_memory(self, needs) -> int:
         """The pool size that the free device memory allows: windowed groups take what their windows
         need (``CacheManager.pages_of_group``), the rest goes to the groups that keep every key."""
-        from ..config.spec import PagedCacheNeed
+        from ..config.spec import CompositeCacheNeed, PagedCacheNeed
+        needs = [m for n in needs for m in (n.flat() if isinstance(n, CompositeCacheNeed) else [n])]
         cfg = self.config
         page, step = cfg.kvcache_block_size, max(cfg.max_num_batched_tokens, cfg.max_num_seqs)
         per_page = CacheManager.bytes_per_page(needs, page, self.model.ctx.dtype)
@@ -98,7 +99,8 @@ class ModelRunner:
             return 1
         paged = [n for n in needs if isinstance(n, PagedCacheNeed)]
         windowed = [n for n in paged if n.window is not None] if any(n.window is None for n in paged) else []
-        fixed = sum(CacheManager.pages_of_group(n.window, page, 1 << 30, cfg.max_num_seqs, step) * CacheManager.bytes_per_page([n], page, self.model.ctx.dtype)
+        elt = torch.empty((), dtype=self.model.ctx.dtype).element_size()
+        fixed = sum(CacheManager.pages_of_group(n.window, page, 1 << 30, cfg.max_num_seqs, step) * 2 * n.num_kv_heads * page * n.head_dim * elt
                     for n in windowed)
         free, total = torch.cuda.mem_get_info(self.device)
         budget = free - int(total * (1.0 - cfg.gpu_memory_utilization)) - (2 << 30) - fixed  # room for activations
@@ -181,7 +183,7 @@ class ModelRunner:
         token_ids = np.zeros(bucket, np.int32)
         positions = np.zeros(bucket, np.int32)
         ctx_len = np.ones(bucket, np.int32)
-        slots = np.zeros(bucket, np.int32)
+        slots = np.full(bucket, cache.spare_slot, np.int32)      # padding rows keep their state in the spare slot
         token_ids[:S], positions[:S], ctx_len[:S], slots[:S] = tok, pos, ctx, slot
         tables = []
         for g in range(cache.num_groups()):
@@ -267,7 +269,7 @@ class ModelRunner:
         starts = np.full(Sb + 1, Tb, np.int32)
         starts[:Hb + 1] = np.arange(Hb + 1, dtype=np.int32)
         starts[Hb:S + extra + 1] = q_start[head:] + extra
-        ctx_len, slots = np.ones(Sb, np.int32), np.zeros(Sb, np.int32)
+        ctx_len, slots = np.ones(Sb, np.int32), np.full(Sb, cache.spare_slot, np.int32)     # padding requests keep their state in the spare slot
         ctx_len[:head], slots[:head] = ctx[:head], slot[:head]
         ctx_len[Hb:S + extra], slots[Hb:S + extra] = ctx[head:], slot[head:]
         logit_rows = np.full(Rb, 0, np.int32)

@@ -95,6 +95,87 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status:
     return out
 
 
+def embedding_scaled(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float, status: Optional[torch.Tensor] = None,
+                     pairs: Optional[torch.Tensor] = None, mul_prev: int = 0, mul_cur: int = 0, positions: Optional[torch.Tensor] = None,
+                     seq_of_token: Optional[torch.Tensor] = None, q_start: Optional[torch.Tensor] = None, state_slot: Optional[torch.Tensor] = None,
+                     prev_state: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[t] = table[ids[t]] * scale`` and, with ``pairs [buckets + 1, H]``, ``+ pairs[row]`` where ``row`` is
+    ``(previous token * mul_prev + ids[t] * mul_cur) mod buckets``, or ``buckets`` at position 0.  The token before a
+    portion's first one is read from ``prev_state [slots]`` (int32, row ``state_slot[seq]``), which then takes the
+    portion's last token."""
+    _check(table, "embedding table", ndim=2)
+    _check(ids, "token ids", torch.int32, 1)
+    _check(out, "embedding output", torch.float32, 2)
+    T, (V, H) = ids.shape[0], table.shape
+    if tuple(out.shape) != (T, H):
+        raise KernelError(f"embedding output: expected shape {(T, H)}, found {tuple(out.shape)}")
+    buckets = slots = 0
+    if pairs is not None:
+        _check(pairs, "pair table", ndim=2)
+        if pairs.shape[1] != H or pairs.shape[0] < 2:
+            raise KernelError(f"pair table: expected [buckets + 1, {H}], found {tuple(pairs.shape)}")
+        buckets = pairs.shape[0] - 1
+        for t, what in ((positions, "positions"), (seq_of_token, "seq_of_token"), (q_start, "q_start"), (state_slot, "state_slot")):
+            _check(t, what, torch.int32, 1)
+        _check(prev_state, "previous-token state", torch.int32)
+        slots = prev_state.numel()
+        if positions.shape[0] != T or seq_of_token.shape[0] != T:
+            raise KernelError("embedding: positions and seq_of_token must have one entry per token")
+    _call("embedding", "spy_embedding_scaled", _ptr(table), _code(table, "embedding table"), _ptr(ids), _ptr(out), T, H, V, ctypes.c_float(scale),
+          _ptr(pairs), _code(pairs, "pair table") if pairs is not None else 0, ctypes.c_longlong(buckets), ctypes.c_longlong(int(mul_prev)),
+          ctypes.c_longlong(int(mul_cur)), _ptr(positions), _ptr(seq_of_token), _ptr(q_start), _ptr(state_slot), _ptr(prev_state), slots,
+          _ptr(status), _stream())
+    return out
+
+
+def _stack_of(delta: Optional[torch.Tensor], like: torch.Tensor, what: str):
+    """(pointer argument, parts, elements between parts) of a delta that is None, ``like``'s shape, or a stack of it."""
+    if delta is None:
+        return None, 0, 0
+    if delta.dim() == 3:
+        _check(delta, what, ndim=3)
+        if tuple(delta.shape[1:]) != tuple(like.shape):
+            raise KernelError(f"{what}: stacked shape {tuple(delta.shape)} does not fit {tuple(like.shape)}")
+        return delta, delta.shape[0], delta.shape[1] * delta.shape[2]
+    _check(delta, what, ndim=2)
+    if tuple(delta.shape) != tuple(like.shape):
+        raise KernelError(f"{what}: shape {tuple(delta.shape)} differs from {tuple(like.shape)}")
+    return delta, 1, 0
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, delta: Optional[torch.Tensor] = None, delta_scale: float = 1.0,
+              delta2: Optional[torch.Tensor] = None, delta2_scale: float = 1.0, rows: Optional[torch.Tensor] = None, write_back: bool = False,
+              center: bool = True) -> torch.Tensor:
+    """``out = layer_norm(x + delta_scale * delta + delta2_scale * delta2) * weight`` row by row (mean removed, no bias;
+    ``center=False``: the mean stays, an RMS norm); with ``write_back`` the sum is stored into ``x``; ``rows`` gathers rows.
+    Each delta has x's shape or is a stack ``[splits, rows, len]`` of partial sums that are added in order; both have
+    one dtype."""
+    _check(x, "layernorm input", ndim=2)
+    _check(weight, "layernorm weight", ndim=1)
+    _check(out, "layernorm output", ndim=2)
+    H = x.shape[1]
+    if weight.shape[0] != H or out.shape[1] != H:
+        raise KernelError(f"layernorm: row lengths differ: input {H}, weight {weight.shape[0]}, output {out.shape[1]}")
+    if delta is None and delta2 is not None:
+        delta, delta_scale, delta2, delta2_scale = delta2, delta2_scale, None, 1.0
+    a, a_splits, a_stride = _stack_of(delta, x, "layernorm delta")
+    b, b_splits, b_stride = _stack_of(delta2, x, "layernorm second delta")
+    if a is not None and b is not None and a.dtype != b.dtype:
+        raise KernelError(f"layernorm: the two deltas differ in dtype ({a.dtype}, {b.dtype})")
+    if rows is not None:
+        _check(rows, "layernorm rows", torch.int32, 1)
+        n = rows.shape[0]
+    else:
+        n = x.shape[0]
+    if out.shape[0] != n:
+        raise KernelError(f"layernorm: output has {out.shape[0]} rows, expected {n}")
+    _call("layernorm", "spy_layernorm", _ptr(x), _code(x, "layernorm input"), _ptr(a), a_splits, ctypes.c_longlong(a_stride), ctypes.c_float(delta_scale),
+          _ptr(b), b_splits, ctypes.c_longlong(b_stride), ctypes.c_float(delta2_scale), _code(a, "layernorm delta") if a is not None else 0,
+          _ptr(rows), _ptr(weight), _code(weight, "layernorm weight"), _ptr(out), _code(out, "layernorm output"), n, H, ctypes.c_float(eps),
+          int(bool(write_back)), int(bool(center)), _stream())
+    return out
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, delta: Optional[torch.Tensor] = None,
             rows: Optional[torch.Tensor] = None, write_back: bool = False) -> torch.Tensor:
     """``out = rmsnorm(x [+ delta]) * weight`` row by row; with ``write_back`` the sum is stored
@@ -231,6 +312,159 @@ def attention_generic(q: torch.Tensor, num_heads: int, head_dim: int, out: torch
     _call("attention_generic", "spy_attention_generic", _ptr(q), ctypes.c_longlong(q.shape[1]), _ptr(out), _code(q, "attention queries"),
           _ptr(pages), _code(pages, "cache pages"), _ptr(block_table), block_table.shape[1], page_size, num_pages, num_heads, nkv, head_dim,
           _ptr(positions), _ptr(seq_of_token), T, int(window or 0), ctypes.c_float(scale), _ptr(status), _stream())
+    return out
+
+
+def scaled_sum(out: torch.Tensor, a: torch.Tensor, a_scale: float, b: torch.Tensor, b_scale: float) -> torch.Tensor:
+    """``out = a_scale * a + b_scale * b`` in 32-bit; ``a`` and ``b`` have out's shape or are stacks of partial sums (one dtype)."""
+    _check(out, "weighted sum", torch.float32, 2)
+    if a.dtype != b.dtype:
+        a, b = (t.float() if t.dim() == 2 else t for t in (a, b))
+    pa, sa, stride_a = _stack_of(a, out, "first result")
+    pb, sb, stride_b = _stack_of(b, out, "second result")
+    if pa.dtype != pb.dtype:
+        raise KernelError(f"scaled_sum: the two results differ in dtype ({pa.dtype}, {pb.dtype})")
+    _call("layernorm", "spy_scaled_sum", _ptr(out), _ptr(pa), sa, ctypes.c_longlong(stride_a), ctypes.c_float(a_scale), _ptr(pb), sb,
+          ctypes.c_longlong(stride_b), ctypes.c_float(b_scale), _code(pa, "first result"), ctypes.c_longlong(out.numel()), _stream())
+    return out
+
+
+def _paged(pages: torch.Tensor, what: str, head_dim: int):
+    _check(pages, what, ndim=5)
+    num_pages, two, nkv, page_size, hd = pages.shape
+    if two != 2 or hd != head_dim:
+        raise KernelError(f"{what}: expected [pages, 2, nkv, page_size, {head_dim}], found {tuple(pages.shape)}")
+    return num_pages, nkv, page_size
+
+
+def pool_store(pages: torch.Tensor, block_table: torch.Tensor, pooled: torch.Tensor, pool_table: torch.Tensor, pool: int, positions: torch.Tensor,
+               seq_of_token: torch.Tensor, status: Optional[torch.Tensor] = None) -> None:
+    """For every token of the batch whose position ends a block of ``pool`` tokens: the means of the block's keys and of its
+    values, read from ``pages`` through ``block_table``, go to entry ``position // pool`` of ``pooled`` through ``pool_table``."""
+    hd = pages.shape[-1]
+    num_pages, nkv, page_size = _paged(pages, "cache pages", hd)
+    num_pooled, nkv2, page_size2 = _paged(pooled, "pooled pages", hd)
+    if (nkv2, page_size2) != (nkv, page_size) or pooled.dtype != pages.dtype:
+        raise KernelError("pool_store: the pooled cache must have the token cache's heads, page size and dtype")
+    _check(block_table, "block table", torch.int32, 2)
+    _check(pool_table, "pooled block table", torch.int32, 2)
+    _check(positions, "positions", torch.int32, 1)
+    _check(seq_of_token, "seq_of_token", torch.int32, 1)
+    if block_table.shape != pool_table.shape:
+        raise KernelError("pool_store: the two block tables must have one shape")
+    _call("attention_pool", "spy_pool_store", _ptr(pages), num_pages, _ptr(block_table), _ptr(pooled), num_pooled, _ptr(pool_table), block_table.shape[1],
+          page_size, nkv, hd, _code(pages, "cache pages"), int(pool), _ptr(positions), _ptr(seq_of_token), positions.shape[0], _ptr(status), _stream())
+
+
+def attention_pool(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
+                   pooled: Optional[torch.Tensor], pool_table: Optional[torch.Tensor], positions: torch.Tensor, seq_of_token: torch.Tensor, scale: float,
+                   window: int, pool: int, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of every token of the batch over the last ``window`` keys of its sequence and one pooled entry for every
+    block of ``pool`` tokens that ends at least ``window`` positions before it (``pool`` 0: none), under one softmax.
+    ``q [T, >= nh*hd]``, ``out [T, nh*hd]``."""
+    _check(q, "attention queries", ndim=2)
+    _check(out, "attention output", q.dtype, 2)
+    num_pages, nkv, page_size = _paged(pages, "cache pages", head_dim)
+    _check(block_table, "block table", torch.int32, 2)
+    _check(positions, "positions", torch.int32, 1)
+    _check(seq_of_token, "seq_of_token", torch.int32, 1)
+    T = q.shape[0]
+    if q.shape[1] < num_heads * head_dim or tuple(out.shape) != (T, num_heads * head_dim):
+        raise KernelError(f"attention: q {tuple(q.shape)} / out {tuple(out.shape)} do not fit {num_heads} heads of {head_dim}")
+    if positions.shape[0] != T or seq_of_token.shape[0] != T:
+        raise KernelError("attention: positions and seq_of_token must have one entry per token")
+    num_pooled = 0
+    if pool:
+        num_pooled, nkv2, page_size2 = _paged(pooled, "pooled pages", head_dim)
+        _check(pool_table, "pooled block table", torch.int32, 2)
+        if (nkv2, page_size2) != (nkv, page_size) or pooled.dtype != pages.dtype or pool_table.shape != block_table.shape:
+            raise KernelError("attention: the pooled cache must have the token cache's heads, page size, dtype and table shape")
+    _call("attention_pool", "spy_attention_pool", _ptr(q), ctypes.c_longlong(q.shape[1]), _ptr(out), _code(q, "attention queries"), _ptr(pages), num_pages,
+          _ptr(block_table), _ptr(pooled if pool else None), num_pooled, _ptr(pool_table if pool else None), _code(pages, "cache pages"),
+          block_table.shape[1], page_size, num_heads, nkv, head_dim, _ptr(positions), _ptr(seq_of_token), T, int(window), int(pool or 0),
+          ctypes.c_float(scale), _ptr(status), _stream())
+    return out
+
+
+def mlstm_record(dk: int, dv: int) -> int:
+    """Floats of one head's state of the gated matrix memory (the matrix, and the normaliser vector and running maximum once per column tile)."""
+    lib = build.load("recurrence")
+    lib.spy_mlstm_record.restype = ctypes.c_longlong
+    return int(lib.spy_mlstm_record(int(dk), int(dv)))
+
+
+def _scan_common(proj, state, q_start, state_slot, out, heads, dv):
+    _check(proj, "fused projection", torch.float32, 2)
+    _check(state, "recurrent state", torch.float32)
+    _check(q_start, "q_start", torch.int32, 1)
+    _check(state_slot, "state_slot", torch.int32, 1)
+    _check(out, "recurrence output", torch.float32, 2)
+    if tuple(out.shape) != (proj.shape[0], heads * dv):
+        raise KernelError(f"recurrence output: expected {(proj.shape[0], heads * dv)}, found {tuple(out.shape)}")
+
+
+def mlstm_scan(proj: torch.Tensor, offsets, bias_i: torch.Tensor, bias_f: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor,
+               state_slot: torch.Tensor, num_seqs: int, out: torch.Tensor, heads: int, dk: int, dv: int, q_scale: float, cap: float,
+               status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The gated matrix memory over every request's tokens of this step, in order, from and into ``state [slots, heads * record]``.
+    ``proj [T, ld]`` float32 holds q, k, v and the two gates' pre-activations at the columns ``offsets = (q, k, v, i, f)``."""
+    _scan_common(proj, state, q_start, state_slot, out, heads, dv)
+    if state.dim() != 2 or state.shape[1] != heads * mlstm_record(dk, dv):
+        raise KernelError(f"mlstm: state {tuple(state.shape)} does not fit {heads} heads of {dk} x {dv}")
+    _check(bias_i, "input gate bias", torch.float32, 1)
+    _check(bias_f, "forget gate bias", torch.float32, 1)
+    oq, ok, ov, oi, of = (int(o) for o in offsets)
+    if max(oq + heads * dk, ok + heads * dk, ov + heads * dv, oi + heads, of + heads) > proj.shape[1] or bias_i.shape[0] != heads or bias_f.shape[0] != heads:
+        raise KernelError("mlstm: the column offsets or the biases do not fit the projection")
+    _call("recurrence", "spy_mlstm_scan", _ptr(proj), ctypes.c_longlong(proj.shape[1]), oq, ok, ov, oi, of, _ptr(bias_i), _ptr(bias_f), _ptr(state),
+          state.shape[0], _ptr(q_start), _ptr(state_slot), int(num_seqs), _ptr(out), heads, dk, dv, ctypes.c_float(q_scale), ctypes.c_float(cap),
+          _ptr(status), _stream())
+    return out
+
+
+def delta_scan(proj: torch.Tensor, offsets, decay_pre: torch.Tensor, bias_a: torch.Tensor, decay_offset: torch.Tensor, state: torch.Tensor,
+               q_start: torch.Tensor, state_slot: torch.Tensor, num_seqs: int, out: torch.Tensor, heads: int, dk: int,
+               status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The generalised delta rule over every request's tokens of this step, from and into ``state [slots, heads * dk * dk]``.
+    ``proj [T, ld]`` float32 holds r, k, v and the removal rate's pre-activation at ``offsets = (r, k, v, a)``;
+    ``decay_pre [T, heads * dk]`` the decay's pre-activation."""
+    _scan_common(proj, state, q_start, state_slot, out, heads, dk)
+    if state.dim() != 2 or state.shape[1] != heads * dk * dk:
+        raise KernelError(f"delta rule: state {tuple(state.shape)} does not fit {heads} heads of {dk} x {dk}")
+    _check(decay_pre, "decay pre-activation", torch.float32, 2)
+    _check(bias_a, "removal rate bias", torch.float32, 1)
+    _check(decay_offset, "decay offset", torch.float32, 1)
+    o_r, ok, ov, oa = (int(o) for o in offsets)
+    n = heads * dk
+    if max(o_r, ok, ov, oa) + n > proj.shape[1] or tuple(decay_pre.shape) != (proj.shape[0], n) or bias_a.shape[0] != n or decay_offset.shape[0] != n:
+        raise KernelError("delta rule: the column offsets, the decay or the biases do not fit the projection")
+    _call("recurrence", "spy_delta_scan", _ptr(proj), ctypes.c_longlong(proj.shape[1]), o_r, ok, ov, oa, _ptr(decay_pre), _ptr(bias_a), _ptr(decay_offset),
+          _ptr(state), state.shape[0], _ptr(q_start), _ptr(state_slot), int(num_seqs), _ptr(out), heads, dk, _ptr(status), _stream())
+    return out
+
+
+def gated_head_norm(o: torch.Tensor, proj: torch.Tensor, gate_offset: int, weight: torch.Tensor, out: torch.Tensor, heads: int, dv: int, eps: float) -> torch.Tensor:
+    """``out = o / rms(o per head) * weight * sigmoid(proj[:, gate_offset : gate_offset + heads * dv])``; ``o`` float32 ``[T, heads * dv]``."""
+    _check(o, "recurrence output", torch.float32, 2)
+    _check(proj, "fused projection", torch.float32, 2)
+    _check(weight, "head norm weight", torch.float32, 1)
+    _check(out, "gated output", ndim=2)
+    n = heads * dv
+    if o.shape[1] != n or tuple(out.shape) != tuple(o.shape) or weight.shape[0] != n or gate_offset + n > proj.shape[1] or proj.shape[0] != o.shape[0]:
+        raise KernelError("gated_head_norm: shapes do not fit")
+    _call("recurrence", "spy_gated_head_norm", _ptr(o), _ptr(proj), ctypes.c_longlong(proj.shape[1]), int(gate_offset), _ptr(weight), _ptr(out),
+          _code(out, "gated output"), o.shape[0], heads, dv, ctypes.c_float(eps), _stream())
+    return out
+
+
+def tanh_cols(proj: torch.Tensor, offset: int, n: int, out: torch.Tensor) -> torch.Tensor:
+    """``out[t, j] = tanh(proj[t, offset + j])`` for ``j < n``; proj float32."""
+    _check(proj, "fused projection", torch.float32, 2)
+    _check(out, "tanh output", ndim=2)
+    if offset + n > proj.shape[1] or tuple(out.shape) != (proj.shape[0], n):
+        raise KernelError("tanh_cols: shapes do not fit")
+    _call("recurrence", "spy_tanh_cols", _ptr(proj), ctypes.c_longlong(proj.shape[1]), int(offset), int(n), _ptr(out), _code(out, "tanh output"),
+          proj.shape[0], _stream())
     return out
 
 

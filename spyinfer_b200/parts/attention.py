@@ -15,7 +15,7 @@ import math
 import torch
 
 from .. import kernels
-from ..config.spec import PagedCacheNeed
+from ..config.spec import CompositeCacheNeed, PagedCacheNeed
 from ..weights.loader import WeightDecl
 from .base import Mixer
 from .linear import Linear
@@ -161,4 +161,87 @@ class Attention(Mixer):
             # the float32 path, head sizes above 128 or no multiple of 8, more than 16 query heads a key/value head
             kernels.attention_generic(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.seq_of_token,
                                       self.scale, window=self.window, status=batch.status)
+        return self.o(out, defer=self.defer_output)
+
+
+@register_part("pooled_window_attention")
+class PooledWindowAttention(Attention):
+    """Grouped-query attention over a window of the last ``window`` keys plus one pooled key and value for every block
+    of ``pool`` tokens that lies wholly before the window (the means of the block's keys and values as the cache holds
+    them), all under one softmax.  A token that has left the window while its block is not yet wholly before it is
+    seen by no query.
+
+    params, beside those of ``attention`` that it shares (``hidden_size``, ``num_heads``, ``num_kv_heads``,
+    ``head_dim``, ``position``, ``scale``, ``prefix``): ``window``, ``pool`` (0 or None: no pooled entries),
+    ``values_are_keys`` (true: there is no value projection, a token's value is its key as projected, before the
+    position encoding) and ``names`` (the projections' tensor names: ``q``, ``k``, ``v``, ``o``).
+
+    The pooled entries live in a paged cache of their own with one entry for every ``pool`` tokens; an entry is made,
+    from the token cache, in the step that stores its block's last token, which is why the token cache keeps
+    ``max(window, pool)`` positions."""
+
+    graph_safe = True
+
+    def __init__(self, params, ctx):
+        base = dict(params)
+        base.setdefault("qk_norm_eps", None)
+        super().__init__(base, ctx)
+        if self.window is None:
+            raise ValueError("pooled_window_attention: a window is required")
+        self.window = int(self.window)
+        self.pool = int(params.get("pool") or 0)
+        if self.pool < 0:
+            raise ValueError(f"pooled_window_attention: pool {self.pool} must not be negative")
+        self.values_are_keys = bool(params.get("values_are_keys", False))
+        names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight"}
+        names.update(params.get("names") or {})
+        self.names = names
+
+    def weight_decls(self):
+        p, nh, nkv, hd, H, n = self.prefix, self.nh, self.nkv, self.hd, self.hidden, self.names
+        decls = [WeightDecl(p + n["q"], (nh * hd, H)), WeightDecl(p + n["k"], (nkv * hd, H))]
+        if not self.values_are_keys:
+            decls.append(WeightDecl(p + n["v"], (nkv * hd, H)))
+        return decls + [WeightDecl(p + n["o"], (H, nh * hd))]
+
+    def bind(self, tensors):
+        p, n = self.prefix, self.names
+        q, k = tensors[p + n["q"]], tensors[p + n["k"]]
+        v = k if self.values_are_keys else tensors[p + n["v"]]     # the key projection's rows once more: the value IS the key before rotation
+        qkv = [q, k, v]
+        if len({t.dtype for t in qkv}) > 1:
+            qkv = [t.float() for t in qkv]
+        self.qkv = Linear(torch.cat(qkv, dim=0).contiguous(), self.ctx.dtype)
+        self.o = Linear(tensors[p + n["o"]], self.ctx.dtype)
+
+    def modules(self):
+        mods = ["qk_rope_store", "attention_pool"] + self.qkv.modules() + self.o.modules()
+        if self.position is not None:
+            mods += self.position.modules()
+        return mods
+
+    def cache_need(self):
+        if not self.pool:
+            return PagedCacheNeed(self.nkv, self.hd, self.window)
+        return CompositeCacheNeed((PagedCacheNeed(self.nkv, self.hd, max(self.window, self.pool)),
+                                   PagedCacheNeed(self.nkv, self.hd, None, stride=self.pool)))
+
+    def forward(self, x, batch, cache):
+        if self.rope_table is None and self.position is not None:
+            self.rope_table = self.position.rotation_table()
+        tokens, pooled = (cache.parts[0], cache.parts[1]) if self.pool else (cache, None)
+        qkv = self.qkv(x, defer=True)
+        q = None
+        if qkv.dim() == 3:
+            q = torch.empty((x.shape[0], self.nh * self.hd), dtype=x.dtype, device=x.device)
+        q = kernels.qk_rope_store(qkv, self.nh, self.nkv, self.hd, None, None, 0.0, self.rope_table, batch.positions, batch.seq_of_token,
+                                  tokens.block_table, tokens.pages, store=tokens.writes, status=batch.status, q_out=q,
+                                  pairing=self.position.pairing if self.position is not None else "half")
+        if self.pool and pooled.writes:
+            kernels.pool_store(tokens.pages, tokens.block_table, pooled.pages, pooled.block_table, self.pool, batch.positions, batch.seq_of_token,
+                               status=batch.status)
+        out = torch.empty((x.shape[0], self.nh * self.hd), dtype=x.dtype, device=x.device)
+        kernels.attention_pool(q, self.nh, self.hd, out, tokens.pages, tokens.block_table, pooled.pages if self.pool else None,
+                               pooled.block_table if self.pool else None, batch.positions, batch.seq_of_token, self.scale, self.window, self.pool,
+                               status=batch.status)
         return self.o(out, defer=self.defer_output)

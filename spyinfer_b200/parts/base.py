@@ -17,7 +17,7 @@ parts the model has.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Dict, List, Optional, Sequence
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -32,6 +32,15 @@ class BuildContext:
     dtype: torch.dtype
     device: torch.device
     max_model_len: int
+
+
+@dataclass
+class ScaledParts:
+    """A result that is still a weighted sum, ``sum_i scale_i * term_i``: each term is ``[rows, size]`` or a stack
+    ``[splits, rows, size]`` of float32 partial products.  A mixer made of several mixers side by side hands this on,
+    and a norm that says ``takes_scaled_parts`` adds it to the residual in its own kernel."""
+
+    terms: List[Tuple[torch.Tensor, float]]
 
 
 class Part:
@@ -65,6 +74,9 @@ class Part:
 
 
 class Norm(Part):
+    #: True: ``forward_add`` also takes a ``ScaledParts`` as ``delta`` and a ``scale`` other than 1
+    takes_scaled_parts: bool = False
+
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         raise NotImplementedError
 
@@ -73,7 +85,9 @@ class Norm(Part):
         """``residual += delta`` (32-bit, in place, skipped when ``delta`` is None), then the
         norm of the sum.  With ``rows`` only those rows are normed and nothing is written back.
         ``delta`` is ``[rows, size]``, or a stack ``[splits, rows, size]`` of float32 partial
-        products (a mixer or feed-forward may hand its last product over unsummed); all are added."""
+        products (a mixer or feed-forward may hand its last product over unsummed); all are added.
+        A norm that ``takes_scaled_parts`` has one more argument, ``scale`` (default 1): the residual
+        takes ``scale * delta``, and ``delta`` may be a ``ScaledParts``."""
         raise NotImplementedError
 
 
@@ -121,7 +135,12 @@ class Block:
     required: Sequence[str] = ("mixer_norm", "mixer", "ffn_norm", "feed_forward")
     optional: Sequence[str] = ()
 
-    def __init__(self, parts: Dict[str, Part]):
+    #: what the residual stream takes of a part's output (``hidden += residual_scale * part(norm(hidden))``); the model
+    #: hands the last block's to the final norm
+    residual_scale: float = 1.0
+
+    def __init__(self, parts: Dict[str, Part], params: Optional[Dict[str, Any]] = None):
+        self.params = dict(params or {})
         missing = [r for r in self.required if r not in parts]
         unknown = [r for r in parts if r not in self.required and r not in self.optional]
         if missing or unknown:

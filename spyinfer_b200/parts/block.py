@@ -21,11 +21,13 @@ def register_block(kind: str):
     return wrap
 
 
-def build_block(kind: str, parts) -> Block:
-    """``parts``: role -> built part (``LayerSpec.roles()`` with every ``PartSpec`` built)."""
+def build_block(kind: str, parts, params=None) -> Block:
+    """``parts``: role -> built part (``LayerSpec.roles()`` with every ``PartSpec`` built); ``params``: the
+    arrangement's own constants (``LayerSpec.block_params``)."""
     if kind not in _BLOCKS:
         raise KeyError(f"unknown block arrangement {kind!r}; registered: {', '.join(sorted(_BLOCKS))}")
-    return _BLOCKS[kind](dict(parts))
+    cls = _BLOCKS[kind]
+    return cls(dict(parts), dict(params)) if params else cls(dict(parts))
 
 
 @register_block("pre_norm")
@@ -36,4 +38,34 @@ class PreNormBlock(Block):
         x = self.mixer_norm.forward_add(hidden, delta)
         a = self.mixer.forward(x, batch, cache)
         x = self.ffn_norm.forward_add(hidden, a)
+        return hidden, self.feed_forward.forward(x)
+
+
+@register_block("pre_norm_scaled")
+class ScaledPreNormBlock(Block):
+    """``h += m * mixer(norm(h)); h += m * ffn(norm(h))`` with one multiplier ``m`` (param ``residual_scale``) for both
+    sums, and a layer may do without the feed-forward half.  Its norms must take a scale (``Norm.takes_scaled_parts``);
+    then the mixer may also hand over a weighted sum that is still to be formed (``ScaledParts``)."""
+
+    graph_safe = True
+    required = ("mixer_norm", "mixer")
+    optional = ("ffn_norm", "feed_forward")
+
+    def __init__(self, parts, params=None):
+        super().__init__(parts, params)
+        self.residual_scale = float(self.params.get("residual_scale", 1.0))
+        if (self.ffn_norm is None) != (self.feed_forward is None):
+            raise ValueError("block arrangement 'pre_norm_scaled': the feed-forward and its norm come together or not at all")
+        for norm in (self.mixer_norm, self.ffn_norm):
+            if norm is not None and not norm.takes_scaled_parts:
+                raise ValueError(f"block arrangement 'pre_norm_scaled': the norm {norm.kind!r} takes no scale")
+        if hasattr(self.mixer, "scaled_parts_ok"):
+            self.mixer.scaled_parts_ok = self.ffn_norm is not None      # the sum is formed by this layer's second norm
+
+    def forward(self, hidden, delta, batch, cache):
+        x = self.mixer_norm.forward_add(hidden, delta, scale=self.residual_scale)
+        a = self.mixer.forward(x, batch, cache)
+        if self.feed_forward is None:
+            return hidden, a
+        x = self.ffn_norm.forward_add(hidden, a, scale=self.residual_scale)
         return hidden, self.feed_forward.forward(x)

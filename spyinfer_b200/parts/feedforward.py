@@ -20,7 +20,8 @@ from .registry import register_part
 @register_part("gated_mlp")
 class GatedMLP(FeedForward):
     graph_safe = True
-    """params: ``hidden_size``, ``intermediate_size``, ``activation`` ("silu"), ``prefix``."""
+    """params: ``hidden_size``, ``intermediate_size``, ``activation`` ("silu"), ``prefix``, ``names`` (the three tensors'
+    names after the prefix: ``gate``, ``up``, ``down``; default ``gate_proj.weight`` and so on)."""
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
@@ -28,18 +29,20 @@ class GatedMLP(FeedForward):
         if params.get("activation", "silu") != "silu":
             raise ValueError(f"gated_mlp: activation {params['activation']!r} is not implemented (only \"silu\")")
         self.prefix = params.get("prefix", "")
+        self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+        self.names.update(params.get("names") or {})
         self.gate_up = self.down = None
         self.fused = False
 
     def weight_decls(self):
-        p = self.prefix
-        return [WeightDecl(p + "gate_proj.weight", (self.inter, self.hidden)),
-                WeightDecl(p + "up_proj.weight", (self.inter, self.hidden)),
-                WeightDecl(p + "down_proj.weight", (self.hidden, self.inter))]
+        p, n = self.prefix, self.names
+        return [WeightDecl(p + n["gate"], (self.inter, self.hidden)),
+                WeightDecl(p + n["up"], (self.inter, self.hidden)),
+                WeightDecl(p + n["down"], (self.hidden, self.inter))]
 
     def bind(self, tensors):
-        p = self.prefix
-        gate, up = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
+        p, n = self.prefix, self.names
+        gate, up = tensors[p + n["gate"]], tensors[p + n["up"]]
         if gate.dtype != up.dtype:
             gate, up = gate.float(), up.float()
         self.fused = (self.ctx.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16
@@ -49,7 +52,7 @@ class GatedMLP(FeedForward):
             self.gate_up = Linear(torch.stack([gate, up], dim=1).reshape(2 * self.inter, self.hidden).contiguous(), self.ctx.dtype)
         else:
             self.gate_up = Linear(torch.cat([gate, up], dim=0).contiguous(), self.ctx.dtype)
-        self.down = Linear(tensors[p + "down_proj.weight"], self.ctx.dtype)
+        self.down = Linear(tensors[p + n["down"]], self.ctx.dtype)
         self.gate_up.hint_next = not self.fused       # fused: the down product follows at once
 
     def linears(self):

@@ -10,7 +10,7 @@ import torch
 
 from .. import kernels
 from ..weights.loader import WeightDecl
-from .base import Norm
+from .base import Norm, ScaledParts
 from .registry import register_part
 
 
@@ -40,3 +40,43 @@ class RMSNorm(Norm):
         n = residual.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n, self.size), dtype=out_dtype or self.ctx.dtype, device=residual.device)
         return kernels.rmsnorm(residual, self.weight, self.eps, out, delta=delta, rows=rows, write_back=delta is not None and rows is None)
+
+
+@register_part("layer_norm")
+class LayerNorm(Norm):
+    """``(x - mean) / sqrt(var + eps) * weight`` with ``var`` the mean squared deviation, statistics in 32-bit, a plain
+    weight and no bias.  params: ``size``, ``eps``, ``weight`` (the tensor's relative name), ``center`` (default true;
+    false keeps the mean: an RMS norm).  The residual sum fused into the kernel may carry a scale and may be a weighted
+    sum of two results (``ScaledParts``): ``residual += scale * (s1 * d1 + s2 * d2)``."""
+
+    graph_safe = True
+    takes_scaled_parts = True
+    kernel_modules = ("layernorm",)
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.size, self.eps, self.weight_name = int(params["size"]), float(params["eps"]), params.get("weight", "weight")
+        self.center = bool(params.get("center", True))
+        self.weight = None
+
+    def weight_decls(self):
+        return [WeightDecl(self.weight_name, (self.size,), init="one_plus_normal")]
+
+    def bind(self, tensors):
+        self.weight = tensors[self.weight_name]
+
+    def forward(self, x, out_dtype=None):
+        out = torch.empty(x.shape, dtype=out_dtype or self.ctx.dtype, device=x.device)
+        return kernels.layernorm(x, self.weight, self.eps, out, center=self.center)
+
+    def forward_add(self, residual, delta, rows=None, out_dtype=None, scale=1.0):
+        n = residual.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty((n, self.size), dtype=out_dtype or self.ctx.dtype, device=residual.device)
+        terms = delta.terms if isinstance(delta, ScaledParts) else ([(delta, 1.0)] if delta is not None else [])
+        if len(terms) > 2:
+            raise ValueError(f"layer_norm: a weighted sum of {len(terms)} results (at most two)")
+        if len(terms) == 2 and terms[0][0].dtype != terms[1][0].dtype:
+            terms = [(t.float() if t.dim() == 2 else t, s) for t, s in terms]
+        (d1, s1), (d2, s2) = (terms + [(None, 1.0), (None, 1.0)])[:2]
+        return kernels.layernorm(residual, self.weight, self.eps, out, delta=d1, delta_scale=scale * s1, delta2=d2, delta2_scale=scale * s2,
+                                 rows=rows, write_back=bool(terms) and rows is None, center=self.center)

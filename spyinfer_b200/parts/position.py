@@ -6,10 +6,16 @@ src/utils/constant_table.hpp:28-41 (table) and src/backends/cpu/cpu_operator.cpp
 (rotation).  ``rotary_interleaved``: the same angles on the pairs ``(2j, 2j + 1)`` (the
 rule the reference's doc/op.md:58-95 describes and its code does not use).  Both take an
 optional ``frequency_scale`` (every frequency divided by it: positions stretched linearly)
-or explicit ``inverse_frequencies`` (one per pair: any other frequency function), so a
+or explicit ``inverse_frequencies`` (one per pair: any other frequency function), or a
+``wavelength_scaling`` (``factor``, ``low``, ``high``, ``original``: with the wavelength
+``l = 2 pi / f``, a frequency stays where ``l < original / high``, becomes ``f / factor`` where
+``l > original / low``, and in between is ``(1 - s) f / factor + s f`` with
+``s = (original / l - low) / (high - low)``), so a
 scaled rotary encoding is a parameter, not a new kernel.  ``no_position``: nothing is applied.
 """
 from __future__ import annotations
+
+import math
 
 import torch
 
@@ -24,8 +30,9 @@ _TABLES = {}
 class RotaryHalf(PositionEncoding):
     graph_safe = True
     """params: ``theta``, ``rotary_dim`` (even, at most the head size); optional
-    ``frequency_scale`` (default 1) and ``inverse_frequencies`` (a list of ``rotary_dim / 2``
-    numbers that replaces ``theta^(-j/r)``)."""
+    ``frequency_scale`` (default 1), ``inverse_frequencies`` (a list of ``rotary_dim / 2``
+    numbers that replaces ``theta^(-j/r)``) and ``wavelength_scaling`` (see the module's header;
+    with it the frequencies are worked out in 64-bit and rounded once)."""
 
     kernel_modules = ("qk_rope_store",)
 
@@ -40,10 +47,29 @@ class RotaryHalf(PositionEncoding):
         self.given = params.get("inverse_frequencies")
         if self.given is not None and len(self.given) != self.rotary_dim // 2:
             raise ValueError(f"inverse_frequencies must name {self.rotary_dim // 2} frequencies, found {len(self.given)}")
+        self.bands = params.get("wavelength_scaling")
+        if self.bands is not None:
+            b = {k: float(self.bands[k]) for k in ("factor", "low", "high", "original")}
+            if not (b["factor"] > 0.0 and b["original"] > 0.0 and b["high"] > b["low"] > 0.0):
+                raise ValueError(f"wavelength_scaling needs factor > 0, original > 0 and high > low > 0, found {self.bands}")
+            self.bands = b
 
     def inverse_frequencies(self) -> torch.Tensor:
         r = self.rotary_dim // 2
-        if self.given is not None:
+        if self.bands is not None:
+            b, out = self.bands, []
+            base = [float(f) for f in self.given] if self.given is not None else [self.theta ** (-j / float(r)) for j in range(r)]
+            for f in base:
+                wave = 2.0 * math.pi / f
+                if wave < b["original"] / b["high"]:
+                    out.append(f)
+                elif wave > b["original"] / b["low"]:
+                    out.append(f / b["factor"])
+                else:
+                    s = (b["original"] / wave - b["low"]) / (b["high"] - b["low"])
+                    out.append((1.0 - s) * f / b["factor"] + s * f)
+            inv = torch.tensor(out, dtype=torch.float64).to(torch.float32)
+        elif self.given is not None:
             inv = torch.tensor([float(f) for f in self.given], dtype=torch.float32)
         else:
             j = torch.arange(r, dtype=torch.float32)
@@ -52,7 +78,7 @@ class RotaryHalf(PositionEncoding):
 
     def rotation_table(self):
         key = (self.theta, self.rotary_dim, self.frequency_scale, tuple(self.given) if self.given is not None else None,
-               self.ctx.max_model_len, str(self.ctx.device))
+               tuple(sorted(self.bands.items())) if self.bands is not None else None, self.ctx.max_model_len, str(self.ctx.device))
         if key not in _TABLES:
             inv = self.inverse_frequencies().to(self.ctx.device)
             _TABLES[key] = kernels.build_rope_table(inv, self.ctx.max_model_len)
