@@ -204,3 +204,44 @@ def forward(w, cfg, tokens, compute=torch.float64, store=None, layers_out=None):
         if layers_out is not None:
             layers_out.append(x.clone())
     return lin(layer_norm(x, w["final.norm"], eps), w["head"])
+
+
+def random_weights(cfg, seed, std=0.08, norm_std=0.1, bias_std=0.5):
+    """Seeded bfloat16 tensors with the checkpoint's names for a configuration (``decay_rank`` must be in the
+    configuration of a delta-rule layer)."""
+    g = torch.Generator().manual_seed(seed)
+
+    def mat(*shape, s=std):
+        return (torch.randn(*shape, generator=g) * s).to(torch.bfloat16)
+
+    def gain(n):
+        return (1.0 + torch.randn(n, generator=g) * norm_std).to(torch.bfloat16)
+
+    W, V = cfg["width"], cfg["vocab"]
+    w = {"embed": mat(V, W, s=1.0), "head": mat(V, W), "final.norm": gain(W)}
+    if cfg["embedding"].get("bigram"):
+        w["bigram"] = mat(cfg["embedding"]["bigram"]["buckets"] + 1, W, s=0.5)
+    for i, layer in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", layer["mixer"]
+        w[p + "norm1"] = gain(W)
+        if layer["type"] == "parallel":
+            a, b = m["left"], m["right"]
+            w[p + "mix.left.q"], w[p + "mix.left.k"] = mat(a["heads"] * a["dim"], W, s=2 * std), mat(a["kv_heads"] * a["dim"], W, s=2 * std)
+            w[p + "mix.left.o"] = mat(W, a["heads"] * a["dim"])
+            H, dk, dv = b["heads"], b["dim"], b["vdim"]
+            for n, rows in (("q", H * dk), ("k", H * dk), ("v", H * dv), ("g", H * dv), ("i", H), ("f", H)):
+                w[p + "mix.right." + n] = mat(rows, W)
+            w[p + "mix.right.i.b"], w[p + "mix.right.f.b"] = mat(H, s=bias_std), (2.0 + torch.randn(H, generator=g) * bias_std).to(torch.bfloat16)
+            w[p + "mix.right.norm"], w[p + "mix.right.o"] = gain(H * dv), mat(W, H * dv)
+        else:
+            n, R = m["heads"] * m["dim"], m["decay_rank"]
+            for name in ("r", "k", "v", "g", "a"):
+                w[p + "mix." + name] = mat(n, W)
+            w[p + "mix.a.b"], w[p + "mix.w0"] = mat(n, s=bias_std), mat(n, s=bias_std)
+            w[p + "mix.w1"], w[p + "mix.w2"] = mat(R, W), mat(n, R, s=0.5)
+            w[p + "mix.norm"], w[p + "mix.o"] = gain(n), mat(W, n)
+        if layer.get("mlp"):
+            ff = layer["mlp"]["ff"]
+            w[p + "norm2"] = gain(W)
+            w[p + "mlp.gate"], w[p + "mlp.up"], w[p + "mlp.down"] = mat(ff, W), mat(ff, W), mat(W, ff)
+    return w
