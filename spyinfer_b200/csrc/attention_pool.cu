@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(CHUNK)
 attention_pool_kernel(const TA* __restrict__ q, long long q_row_stride, TA* __restrict__ out, const TC* __restrict__ pages, int num_pages,
                       const int* __restrict__ block_table, const TC* __restrict__ pooled, int num_pooled_pages, const int* __restrict__ pool_table,
                       int table_width, int page_size, int nh, int nkv, int hd, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
-                      int window, int pool, float scale, int* status)
+                      int window, int pool, float scale, const float* __restrict__ lse, int* status)
 {
     extern __shared__ float smem[];
     pdl_enter();
@@ -113,12 +113,16 @@ attention_pool_kernel(const TA* __restrict__ q, long long q_row_stride, TA* __re
     const int* pt = pool_table ? pool_table + (size_t)seq * table_width : nullptr;
     const long long v_offset = (long long)nkv * page_size * hd;  // from a K row to its V row, in both caches
 
+    const int lo = max(0, pos - window + 1);
+    const int nb = (pool > 0 && pos - window + 1 >= pool) ? (pos - window + 1) / pool : 0;   // blocks that end at or before pos - window
+    // lse given: another kernel has done the window's keys (its normalised result is in `out`, the logarithm of its sum of
+    // exponentials in lse); only the pooled entries are walked here and merged with that result at the end
+    const int total = lse != nullptr ? nb : nb + (pos - lo + 1);
+    if (total == 0) return;
+
     const TA* q_row = q + (size_t)t * q_row_stride + (size_t)h * hd;
     for (int d = tid; d < hd; d += CHUNK) q_s[d] = to_f32(q_row[d]);
 
-    const int lo = max(0, pos - window + 1);
-    const int nb = (pool > 0 && pos - window + 1 >= pool) ? (pos - window + 1) / pool : 0;   // blocks that end at or before pos - window
-    const int total = nb + (pos - lo + 1);
     float m = -INFINITY, l = 0.f;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};  // dims tid, tid+128, tid+256, tid+384
     __syncthreads();
@@ -176,6 +180,19 @@ attention_pool_kernel(const TA* __restrict__ q, long long q_row_stride, TA* __re
         __syncthreads();  // p_s and row_s are rewritten by the next chunk
     }
     TA* o_row = out + ((size_t)t * nh + h) * hd;
+    if (lse != nullptr) {
+        const float lw = lse[(size_t)t * nh + h];
+        const float top = fmaxf(lw, m);
+        if (top == -INFINITY) return;
+        const float fw = lw == -INFINITY ? 0.f : expf(lw - top), fp = m == -INFINITY ? 0.f : expf(m - top);
+        const float inv = 1.0f / (fw + l * fp);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int d = tid + r * CHUNK;
+            if (d < hd) o_row[d] = from_f32<TA>((to_f32(o_row[d]) * fw + acc[r] * fp) * inv);
+        }
+        return;
+    }
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
         const int d = tid + r * CHUNK;
@@ -185,13 +202,16 @@ attention_pool_kernel(const TA* __restrict__ q, long long q_row_stride, TA* __re
 
 // q: [T, ...] rows of q_row_stride elements whose first nh*hd elements are the query heads; out: [T, nh*hd];
 // pages / pooled: caches [pages][2][nkv][page_size][hd] of cache_dtype with a block table [S, table_width] each
-// (pool == 0: no pooled entries, pooled and pool_table may be null).
+// (pool == 0: no pooled entries, pooled and pool_table may be null).  lse (null, or [T, nh] float32): the window's keys
+// have been done by another kernel, which left its normalised result in out and the natural logarithm of each row's sum of
+// exponentials in lse; this call then adds the pooled entries to that softmax and rewrites out.
 extern "C" int spy_attention_pool(const void* q, long long q_row_stride, void* out, int act_dtype, const void* pages, int num_pages,
                                   const int* block_table, const void* pooled, int num_pooled_pages, const int* pool_table, int cache_dtype,
                                   int table_width, int page_size, int nh, int nkv, int hd, const int* positions, const int* seq_of_token, int tokens,
-                                  int window, int pool, float scale, int* status, cudaStream_t stream)
+                                  int window, int pool, float scale, const float* lse, int* status, cudaStream_t stream)
 {
     if (tokens <= 0) return 0;
+    if (lse != nullptr && pool <= 0) return 0;   // nothing to merge
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) SPY_FAIL("attention: %d query heads do not group over %d key/value heads", nh, nkv);
     if (hd <= 0 || hd % 4 != 0 || hd > 4 * CHUNK) SPY_FAIL("attention: head_dim %d must be a multiple of 4, at most %d", hd, 4 * CHUNK);
     if (page_size <= 0 || num_pages <= 0 || table_width <= 0) SPY_FAIL("attention: page_size, num_pages and table_width must be positive");
@@ -204,7 +224,7 @@ extern "C" int spy_attention_pool(const void* q, long long q_row_stride, void* o
         SPY_DISPATCH_DTYPE(cache_dtype, TC, {
             spy_launch(attention_pool_kernel<TA, TC>, grid, dim3(CHUNK), smem, stream, (const TA*)q, q_row_stride, (TA*)out, (const TC*)pages, num_pages,
                        block_table, (const TC*)pooled, num_pooled_pages, pool_table, table_width, page_size, nh, nkv, hd, positions, seq_of_token, window,
-                       pool, scale, status);
+                       pool, scale, lse, status);
         })
     })
     SPY_CHECK_LAUNCH("attention_pool");

@@ -69,6 +69,7 @@ struct Params {
     const bf16* q;
     long long q_stride;
     bf16* out;                 // [T, nh * hd]
+    float* lse;                // null, or [T, nh]: the natural logarithm of every row's sum of exp(score) (for a caller that merges further keys in)
     const int* block_table;    // [S, table_width]
     const int* positions;      // [T]
     const int* q_start;        // [S + 1]
@@ -370,6 +371,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
             // ---- ... and this item's output is read and stored meanwhile: O_g / l
             if (my_tiles > 0) {
                 const float inv = l > 0.f ? 1.f / l : 0.f;
+                if (p.lse != nullptr && row_ok) p.lse[(size_t)tok * p.nh + head] = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
                 bf16* dst = p.out + ((size_t)(row_ok ? tok : 0) * p.nh + head) * p.hd;
 #pragma unroll 1
                 for (int c = 0; c < HD; c += 32) {
@@ -535,9 +537,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
 
 
 // Attention of a batch over its pages: prompt portions, any mix, single tokens included.
-extern "C" int spy_attention_tc(const void* q, long long q_row_stride, void* out, const void* pages, const int* block_table, int table_width,
-                                int page_size, int num_pages, int nh, int nkv, int hd, const int* positions, const int* q_start, int tokens,
-                                int seqs, int window, float scale, int* status, cudaStream_t stream)
+static int run_attention_tc(const void* q, long long q_row_stride, void* out, float* lse, const void* pages, const int* block_table, int table_width,
+                            int page_size, int num_pages, int nh, int nkv, int hd, const int* positions, const int* q_start, int tokens,
+                            int seqs, int window, float scale, int* status, cudaStream_t stream)
 {
     if (tokens <= 0 || seqs <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) SPY_FAIL("attention_tc: %d query heads do not group over %d key/value heads", nh, nkv);
@@ -551,7 +553,7 @@ extern "C" int spy_attention_tc(const void* q, long long q_row_stride, void* out
     if (window < 0) SPY_FAIL("attention_tc: window %d must be 0 (none) or positive", window);
     const int Gp = G;   // rows a token takes in a query tile: one per head of the group (128 / G tokens a tile, the remainder of the rows stays empty)
     Params p;
-    p.q = (const bf16*)q; p.q_stride = q_row_stride; p.out = (bf16*)out; p.block_table = block_table;
+    p.q = (const bf16*)q; p.q_stride = q_row_stride; p.out = (bf16*)out; p.lse = lse; p.block_table = block_table;
     p.positions = positions; p.q_start = q_start; p.status = status; p.table_width = table_width; p.page_size = page_size;
     p.num_pages = num_pages; p.nh = nh; p.nkv = nkv; p.G = G; p.Gp = Gp; p.S = seqs; p.window = window; p.hd = hd; p.scale_log2 = scale * LOG2E;
     if (page_size < 8 || page_size > TILE || TILE % page_size != 0)
@@ -589,4 +591,23 @@ extern "C" int spy_attention_tc(const void* q, long long q_row_stride, void* out
     else spy_launch(attention_tc_kernel<128>, grid, dim3(NUM_THREADS), (size_t)Smem<128>::TOTAL, stream, page_map, p);
     SPY_CHECK_LAUNCH("attention_tc");
     return 0;
+}
+
+extern "C" int spy_attention_tc(const void* q, long long q_row_stride, void* out, const void* pages, const int* block_table, int table_width,
+                                int page_size, int num_pages, int nh, int nkv, int hd, const int* positions, const int* q_start, int tokens,
+                                int seqs, int window, float scale, int* status, cudaStream_t stream)
+{
+    return run_attention_tc(q, q_row_stride, out, nullptr, pages, block_table, table_width, page_size, num_pages, nh, nkv, hd, positions, q_start, tokens, seqs,
+                            window, scale, status, stream);
+}
+
+// The same, and lse [tokens, nh] (float32) receives the natural logarithm of every (token, head)'s sum of exp(score * scale):
+// with it a caller can merge further keys into the softmax afterwards.
+extern "C" int spy_attention_tc_lse(const void* q, long long q_row_stride, void* out, float* lse, const void* pages, const int* block_table,
+                                    int table_width, int page_size, int num_pages, int nh, int nkv, int hd, const int* positions, const int* q_start,
+                                    int tokens, int seqs, int window, float scale, int* status, cudaStream_t stream)
+{
+    if (lse == nullptr) SPY_FAIL("attention_tc: no place for the logarithms of the sums");
+    return run_attention_tc(q, q_row_stride, out, lse, pages, block_table, table_width, page_size, num_pages, nh, nkv, hd, positions, q_start, tokens, seqs,
+                            window, scale, status, stream);
 }

@@ -7,7 +7,8 @@
 // and what follows both: each head's output divided by its root mean square, times a weight, times a sigmoid gate.
 //
 // One kernel serves prompt portions and decoding: a block owns CT = 32 value columns of one (request, head), holds its
-// [dk x 32] tile of S in shared memory and walks the request's tokens of this step in order.  The columns of S do not
+// [dk x 32] tile of S in shared memory and walks the request's tokens of this step in order (`longest`: the most tokens a
+// request of the step brings, or more; it only sizes the chunks that are staged in shared memory).  The columns of S do not
 // depend on one another, so the tiles of a head run side by side; the vector n and the maximum m, which all tiles of a head
 // need, are kept and updated by each tile for itself (dk + 1 numbers a tile in the state record: no tile ever reads what
 // another writes, whenever their blocks happen to run).  The per-token arithmetic is the same
@@ -22,19 +23,6 @@ constexpr int CT = 32;   // value columns a block owns
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float log_sigmoidf_(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
-
-// Sum over the block of one value per thread, through `part` (one float a warp); every thread gets the result.
-// Must be followed by a barrier before `part` is written again.
-__device__ __forceinline__ float block_total(float v, float* part)
-{
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    v = warp_sum(v);
-    if (lane == 0) part[warp] = v;
-    __syncthreads();
-    float t = 0.f;
-    for (int w = 0; w < nwarps; ++w) t += part[w];
-    return t;
-}
 
 struct ScanArgs {
     const float* proj;      // [T, ld]
@@ -54,134 +42,175 @@ struct ScanArgs {
     int* status;
 };
 
+constexpr int SP = CT + 4;        // floats between the rows of a state tile in shared memory (4 more than its 32 columns: the 8 x 4 elements a warp touches at a time lie in 32 banks)
+constexpr int THREADS = 256;      // 8 warps; warp w owns the columns 4w .. 4w + 3 of the tile, lane = 4 * (row group) + (column of the four)
+
 template <int MODE>   // 0: gated matrix memory, 1: delta rule
-__global__ void __launch_bounds__(256) scan_kernel(ScanArgs A)
+__global__ void __launch_bounds__(THREADS) scan_kernel(ScanArgs A, int TC)
 {
+    // The tokens of the request are walked in chunks of TC: a chunk's vectors (k, q, and for the delta rule the removal
+    // rate and the decay, with their sigmoids and exponentials) are brought into shared memory by all threads at once; then
+    // every warp walks the chunk's tokens on its own four columns without a barrier (an element of S belongs to one thread,
+    // sums over the rows are three shuffles inside the warp); the chunk's outputs are scaled and stored together.
     extern __shared__ float sm[];
     pdl_enter();
     const int dk = A.dk, dv = A.dv, H = A.H;
-    const int R = blockDim.x / CT;                 // row groups
-    float* S = sm;                                 // [dk][CT]
-    float* k_s = S + (size_t)dk * CT;              // dk
-    float* q_s = k_s + dk;                         // dk
-    float* x1_s = q_s + dk;                        // dk: mLSTM n; delta removal rate
-    float* x2_s = x1_s + dk;                       // dk: delta decay
-    float* red = x2_s + dk;                        // [R][CT]
-    float* red2 = red + R * CT;                    // [R][CT]
-    float* part = red2 + R * CT;                   // 32
+    float* S = sm;                                 // [dk][SP]
+    float* k_s = S + (size_t)dk * SP;              // [TC][dk]
+    float* q_s = k_s + (size_t)TC * dk;            // [TC][dk]
+    float* x1_s = q_s + (size_t)TC * dk;           // delta: removal rate [TC][dk]; memory: n [dk]
+    float* x2_s = x1_s + (MODE == 1 ? (size_t)TC * dk : (size_t)dk);   // delta: decay [TC][dk]; memory: nothing
+    float* v_s = x2_s + (MODE == 1 ? (size_t)TC * dk : 0);             // [TC][CT]
+    float* o_s = v_s + TC * CT;                    // [TC][CT]
+    float* g1_s = o_s + TC * CT;                   // [TC] memory: log input gate; delta: 1 / |k|
+    float* g2_s = g1_s + TC;                       // [TC] memory: log forget gate
+    float* m_s = g2_s + TC;                        // [TC] memory: the running maximum after each token
+    float* nqp = m_s + TC;                         // [TC][8] memory: n . q, one partial sum a warp
 
     const int seq = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * CT;
-    const int tid = threadIdx.x, c = tid % CT, rg = tid / CT;
-    const bool col_ok = c0 + c < dv;
-    const int t0 = A.q_start[seq], t1 = A.q_start[seq + 1];
-    if (t0 >= t1) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int col = warp * 4 + (lane & 3), rg = lane >> 2;         // this thread's column of the tile and its rows rg, rg + 8, ...
+    const int t_begin = A.q_start[seq], t_end = A.q_start[seq + 1];
+    if (t_begin >= t_end) return;
     const int slot = A.state_slot[seq];
     if (slot < 0 || slot >= A.num_slots) {
-        if (tid == 0) report_status(A.status, SPY_STATUS_BAD_PAGE, t0);
+        if (tid == 0) report_status(A.status, SPY_STATUS_BAD_PAGE, t_begin);
         return;
     }
     float* st = A.state + ((size_t)slot * H + h) * A.record;
-    for (int r = rg; r < dk; r += R) S[r * CT + c] = col_ok ? st[(size_t)r * dv + c0 + c] : 0.f;
-    float m = 0.f;
+    for (int idx = tid; idx < dk * CT; idx += THREADS) {
+        const int r = idx / CT, c = idx % CT;
+        S[r * SP + c] = c0 + c < dv ? st[(size_t)r * dv + c0 + c] : 0.f;
+    }
     float* st_nm = st + (size_t)dk * dv + (size_t)blockIdx.z * (dk + 1);      // this tile's own copy of n and m
+    float m = 0.f;
     if (MODE == 0) {
-        for (int r = tid; r < dk; r += blockDim.x) x1_s[r] = st_nm[r];
+        for (int r = tid; r < dk; r += THREADS) x1_s[r] = st_nm[r];
         m = st_nm[dk];
     }
-    __syncthreads();
 
-    for (int t = t0; t < t1; ++t) {
-        const float* row = A.proj + (size_t)t * A.ld;
-        const float v_c = col_ok ? row[A.off_v + h * dv + c0 + c] : 0.f;
-        if (MODE == 0) {
-            // gates, by every thread alike (two numbers a head)
-            const float ig = A.cap * tanhf((row[A.off_x1 + h] + A.bias1[h]) / A.cap);
-            const float fg = log_sigmoidf_(A.cap * tanhf((row[A.off_x2 + h] + A.bias2[h]) / A.cap));
-            const float m_new = fmaxf(fg + m, ig);
-            const float a = expf(fg + m - m_new), b = expf(ig - m_new);
-            m = m_new;
-            float nq = 0.f;
-            for (int r = tid; r < dk; r += blockDim.x) {
-                const float kr = row[A.off_k + h * dk + r], qr = row[A.off_q + h * dk + r] * A.q_scale;
-                const float n = a * x1_s[r] + b * kr;
-                k_s[r] = kr;
-                q_s[r] = qr;
-                x1_s[r] = n;
-                nq += n * qr;
+    for (int t0 = t_begin; t0 < t_end; t0 += TC) {
+        const int n_tok = min(TC, t_end - t0);
+        __syncthreads();                           // the chunk before has been stored (and, the first time, the state is in place)
+        for (int idx = tid; idx < n_tok * dk; idx += THREADS) {
+            const int tt = idx / dk, r = idx - tt * dk, c = h * dk + r;
+            const float* row = A.proj + (size_t)(t0 + tt) * A.ld;
+            k_s[idx] = row[A.off_k + c];
+            q_s[idx] = row[A.off_q + c] * A.q_scale;
+            if (MODE == 1) {
+                x1_s[idx] = sigmoidf_(row[A.off_x1 + c] + A.bias1[c]);
+                x2_s[idx] = expf(-0.60653065971263342f * sigmoidf_(A.extra[(size_t)(t0 + tt) * H * dk + c] + A.bias2[c]));   // exp(-1/2) = 0.6065...
             }
-            nq = block_total(nq, part);            // its barrier also publishes k_s and q_s
-            float acc = 0.f;
-            for (int r = rg; r < dk; r += R) {
-                const float s = a * S[r * CT + c] + (b * k_s[r]) * v_c;
-                S[r * CT + c] = s;
-                acc = fmaf(s, q_s[r], acc);
-            }
-            red[rg * CT + c] = acc;
-            __syncthreads();
-            if (rg == 0 && col_ok) {
-                float o = 0.f;
-                for (int g = 0; g < R; ++g) o += red[g * CT + c];
-                A.out[(size_t)t * H * dv + h * dv + c0 + c] = o / (fmaxf(fabsf(nq), expf(-m)) + 1e-6f);
-            }
-            __syncthreads();                       // k_s, q_s, red and part are rewritten by the next token
-        } else {
-            float ksq = 0.f;
-            for (int r = tid; r < dk; r += blockDim.x) {
-                const int col = h * dk + r;
-                const float kr = row[A.off_k + col];
-                k_s[r] = kr;
-                q_s[r] = row[A.off_q + col];
-                x1_s[r] = sigmoidf_(row[A.off_x1 + col] + A.bias1[col]);
-                x2_s[r] = expf(-0.60653065971263342f * sigmoidf_(A.extra[(size_t)t * H * dk + col] + A.bias2[col]));   // exp(-1/2) = 0.6065...
-                ksq += kr * kr;
-            }
-            ksq = block_total(ksq, part);          // its barrier also publishes the vectors
-            const float inv = 1.0f / sqrtf(ksq + 1e-6f);
-            float us = 0.f;
-            for (int r = rg; r < dk; r += R) us = fmaf(k_s[r] * inv, S[r * CT + c], us);
-            red[rg * CT + c] = us;
-            __syncthreads();
-            us = 0.f;
-            for (int g = 0; g < R; ++g) us += red[g * CT + c];
-            float acc = 0.f;
-            for (int r = rg; r < dk; r += R) {
-                const float u = k_s[r] * inv;
-                const float s = x2_s[r] * S[r * CT + c] - (x1_s[r] * u) * us + k_s[r] * v_c;
-                S[r * CT + c] = s;
-                acc = fmaf(s, q_s[r], acc);
-            }
-            red2[rg * CT + c] = acc;
-            __syncthreads();
-            if (rg == 0 && col_ok) {
-                float o = 0.f;
-                for (int g = 0; g < R; ++g) o += red2[g * CT + c];
-                A.out[(size_t)t * H * dv + h * dv + c0 + c] = o;
+        }
+        for (int idx = tid; idx < n_tok * CT; idx += THREADS) {
+            const int tt = idx / CT, c = idx % CT;
+            v_s[idx] = c0 + c < dv ? A.proj[(size_t)(t0 + tt) * A.ld + A.off_v + h * dv + c0 + c] : 0.f;
+        }
+        if (MODE == 0 && tid < n_tok) {
+            const float* row = A.proj + (size_t)(t0 + tid) * A.ld;
+            g1_s[tid] = A.cap * tanhf((row[A.off_x1 + h] + A.bias1[h]) / A.cap);
+            g2_s[tid] = log_sigmoidf_(A.cap * tanhf((row[A.off_x2 + h] + A.bias2[h]) / A.cap));
+        }
+        __syncthreads();
+        if (MODE == 1) {
+            for (int tt = warp; tt < n_tok; tt += THREADS / 32) {
+                float ksq = 0.f;
+                for (int r = lane; r < dk; r += 32) ksq += k_s[tt * dk + r] * k_s[tt * dk + r];
+                ksq = warp_sum(ksq);
+                if (lane == 0) g1_s[tt] = 1.0f / sqrtf(ksq + 1e-6f);
             }
             __syncthreads();
         }
+        for (int tt = 0; tt < n_tok; ++tt) {
+            const float* k = k_s + tt * dk;
+            const float* q = q_s + tt * dk;
+            const float v_c = v_s[tt * CT + col];
+            float acc = 0.f;
+            if (MODE == 0) {
+                const float ig = g1_s[tt], fg = g2_s[tt];
+                const float m_new = fmaxf(fg + m, ig);
+                const float a = expf(fg + m - m_new), b = expf(ig - m_new);
+                m = m_new;
+                for (int r = rg; r < dk; r += 8) {
+                    const float s = a * S[r * SP + col] + (b * k[r]) * v_c;
+                    S[r * SP + col] = s;
+                    acc = fmaf(s, q[r], acc);
+                }
+                float nq = 0.f;
+                for (int r = tid; r < dk; r += THREADS) {
+                    const float n = a * x1_s[r] + b * k[r];
+                    x1_s[r] = n;
+                    nq += n * q[r];
+                }
+                nq = warp_sum(nq);
+                if (lane == 0) nqp[tt * 8 + warp] = nq;
+                if (tid == 0) m_s[tt] = m;
+            } else {
+                const float inv = g1_s[tt];
+                const float* rate = x1_s + tt * dk;
+                const float* decay = x2_s + tt * dk;
+                float us = 0.f;
+                for (int r = rg; r < dk; r += 8) us = fmaf(k[r] * inv, S[r * SP + col], us);
+                us += __shfl_xor_sync(0xffffffffu, us, 4);
+                us += __shfl_xor_sync(0xffffffffu, us, 8);
+                us += __shfl_xor_sync(0xffffffffu, us, 16);
+                for (int r = rg; r < dk; r += 8) {
+                    const float u = k[r] * inv;
+                    const float s = decay[r] * S[r * SP + col] - (rate[r] * u) * us + k[r] * v_c;
+                    S[r * SP + col] = s;
+                    acc = fmaf(s, q[r], acc);
+                }
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 8);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+            if (rg == 0) o_s[tt * CT + col] = acc;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < n_tok * CT; idx += THREADS) {
+            const int tt = idx / CT, c = idx % CT;
+            if (c0 + c >= dv) continue;
+            float o = o_s[idx];
+            if (MODE == 0) {
+                float nq = 0.f;
+#pragma unroll
+                for (int w = 0; w < 8; ++w) nq += nqp[tt * 8 + w];
+                o = o / (fmaxf(fabsf(nq), expf(-m_s[tt])) + 1e-6f);
+            }
+            A.out[(size_t)(t0 + tt) * H * dv + h * dv + c0 + c] = o;
+        }
     }
-    if (col_ok)
-        for (int r = rg; r < dk; r += R) st[(size_t)r * dv + c0 + c] = S[r * CT + c];
+    __syncthreads();
+    for (int idx = tid; idx < dk * CT; idx += THREADS) {
+        const int r = idx / CT, c = idx % CT;
+        if (c0 + c < dv) st[(size_t)r * dv + c0 + c] = S[r * SP + c];
+    }
     if (MODE == 0) {
-        for (int r = tid; r < dk; r += blockDim.x) st_nm[r] = x1_s[r];
+        for (int r = tid; r < dk; r += THREADS) st_nm[r] = x1_s[r];
         if (tid == 0) st_nm[dk] = m;
     }
 }
 
-static int launch_scan(int mode, ScanArgs& A, int num_seqs, cudaStream_t stream)
+static int launch_scan(int mode, ScanArgs& A, int num_seqs, int longest, cudaStream_t stream)
 {
     if (num_seqs <= 0) return 0;
     if (A.H <= 0 || A.dk <= 0 || A.dv <= 0) SPY_FAIL("recurrence: heads %d, key size %d and value size %d must be positive", A.H, A.dk, A.dv);
     if (A.H > 65535) SPY_FAIL("recurrence: %d heads exceed the grid limit", A.H);
     const int tiles = (A.dv + CT - 1) / CT;
     if (tiles > 65535) SPY_FAIL("recurrence: a value size of %d exceeds the grid limit", A.dv);
-    const int threads = A.dk >= 64 ? 256 : 128;
-    const int R = threads / CT;
-    const size_t smem = ((size_t)A.dk * CT + 4 * (size_t)A.dk + 2 * (size_t)R * CT + 64) * sizeof(float);
+    // tokens a chunk: 16, fewer when a request never brings that many (decoding) or when the vectors of 16 would not fit
+    int tc = 16;
+    while (tc > 1 && tc / 2 >= longest) tc /= 2;
+    auto bytes = [&](int n) {
+        const size_t vectors = mode == 1 ? 4 * (size_t)n * A.dk : 2 * (size_t)n * A.dk + A.dk;
+        return ((size_t)A.dk * SP + vectors + 2 * (size_t)n * CT + 11 * (size_t)n) * sizeof(float);
+    };
+    while (tc > 1 && bytes(tc) > 96 * 1024) tc /= 2;
+    const size_t smem = bytes(tc);
     if (smem > 227 * 1024) SPY_FAIL("recurrence: a key size of %d does not fit a block's shared memory", A.dk);
     auto kernel = mode == 0 ? scan_kernel<0> : scan_kernel<1>;
     if (smem > 48 * 1024) SPY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    spy_launch(kernel, dim3(num_seqs, A.H, tiles), dim3(threads), smem, stream, A);
+    spy_launch(kernel, dim3(num_seqs, A.H, tiles), dim3(THREADS), smem, stream, A, tc);
     SPY_CHECK_LAUNCH("recurrence scan");
     return 0;
 }
@@ -190,22 +219,22 @@ static int launch_scan(int mode, ScanArgs& A, int num_seqs, cudaStream_t stream)
 extern "C" long long spy_mlstm_record(int dk, int dv) { return ((long long)dk * dv + (long long)((dv + CT - 1) / CT) * (dk + 1) + 3) / 4 * 4; }
 
 extern "C" int spy_mlstm_scan(const float* proj, long long ld, int off_q, int off_k, int off_v, int off_i, int off_f, const float* bias_i, const float* bias_f,
-                              float* state, int num_slots, const int* q_start, const int* state_slot, int num_seqs, float* out, int H, int dk, int dv,
-                              float q_scale, float cap, int* status, cudaStream_t stream)
+                              float* state, int num_slots, const int* q_start, const int* state_slot, int num_seqs, int longest, float* out, int H, int dk,
+                              int dv, float q_scale, float cap, int* status, cudaStream_t stream)
 {
     if (!(cap > 0.f)) SPY_FAIL("mlstm: the gates' cap must be positive");
     ScanArgs A = {proj, ld, off_q, off_k, off_v, off_i, off_f, nullptr, bias_i, bias_f, state, spy_mlstm_record(dk, dv), num_slots, q_start, state_slot, out,
                   H, dk, dv, q_scale, cap, status};
-    return launch_scan(0, A, num_seqs, stream);
+    return launch_scan(0, A, num_seqs, longest, stream);
 }
 
 extern "C" int spy_delta_scan(const float* proj, long long ld, int off_r, int off_k, int off_v, int off_a, const float* decay_pre, const float* bias_a,
-                              const float* decay_offset, float* state, int num_slots, const int* q_start, const int* state_slot, int num_seqs, float* out,
-                              int H, int dk, int* status, cudaStream_t stream)
+                              const float* decay_offset, float* state, int num_slots, const int* q_start, const int* state_slot, int num_seqs, int longest,
+                              float* out, int H, int dk, int* status, cudaStream_t stream)
 {
     ScanArgs A = {proj, ld, off_r, off_k, off_v, off_a, 0, decay_pre, bias_a, decay_offset, state, (long long)dk * dk, num_slots, q_start, state_slot, out,
                   H, dk, dk, 1.0f, 1.0f, status};
-    return launch_scan(1, A, num_seqs, stream);
+    return launch_scan(1, A, num_seqs, longest, stream);
 }
 
 // ---- what follows a recurrence: unit root mean square per head, a weight, a sigmoid gate -------------

@@ -358,10 +358,12 @@ def pool_store(pages: torch.Tensor, block_table: torch.Tensor, pooled: torch.Ten
 
 def attention_pool(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
                    pooled: Optional[torch.Tensor], pool_table: Optional[torch.Tensor], positions: torch.Tensor, seq_of_token: torch.Tensor, scale: float,
-                   window: int, pool: int, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   window: int, pool: int, status: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of every token of the batch over the last ``window`` keys of its sequence and one pooled entry for every
     block of ``pool`` tokens that ends at least ``window`` positions before it (``pool`` 0: none), under one softmax.
-    ``q [T, >= nh*hd]``, ``out [T, nh*hd]``."""
+    ``q [T, >= nh*hd]``, ``out [T, nh*hd]``.  With ``lse [T, nh]`` the window's keys have been done already (``out`` holds
+    their normalised result, ``lse`` the logarithm of each row's sum of exponentials, as ``attention_tc`` leaves them) and
+    only the pooled entries are added to that softmax."""
     _check(q, "attention queries", ndim=2)
     _check(out, "attention output", q.dtype, 2)
     num_pages, nkv, page_size = _paged(pages, "cache pages", head_dim)
@@ -379,10 +381,14 @@ def attention_pool(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Te
         _check(pool_table, "pooled block table", torch.int32, 2)
         if (nkv2, page_size2) != (nkv, page_size) or pooled.dtype != pages.dtype or pool_table.shape != block_table.shape:
             raise KernelError("attention: the pooled cache must have the token cache's heads, page size, dtype and table shape")
+    if lse is not None:
+        _check(lse, "logarithms of the sums", torch.float32, 2)
+        if tuple(lse.shape) != (T, num_heads):
+            raise KernelError(f"attention: lse {tuple(lse.shape)} does not fit {T} tokens of {num_heads} heads")
     _call("attention_pool", "spy_attention_pool", _ptr(q), ctypes.c_longlong(q.shape[1]), _ptr(out), _code(q, "attention queries"), _ptr(pages), num_pages,
           _ptr(block_table), _ptr(pooled if pool else None), num_pooled, _ptr(pool_table if pool else None), _code(pages, "cache pages"),
           block_table.shape[1], page_size, num_heads, nkv, head_dim, _ptr(positions), _ptr(seq_of_token), T, int(window), int(pool or 0),
-          ctypes.c_float(scale), _ptr(status), _stream())
+          ctypes.c_float(scale), _ptr(lse), _ptr(status), _stream())
     return out
 
 
@@ -405,9 +411,10 @@ def _scan_common(proj, state, q_start, state_slot, out, heads, dv):
 
 def mlstm_scan(proj: torch.Tensor, offsets, bias_i: torch.Tensor, bias_f: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor,
                state_slot: torch.Tensor, num_seqs: int, out: torch.Tensor, heads: int, dk: int, dv: int, q_scale: float, cap: float,
-               status: Optional[torch.Tensor] = None) -> torch.Tensor:
+               status: Optional[torch.Tensor] = None, longest: Optional[int] = None) -> torch.Tensor:
     """The gated matrix memory over every request's tokens of this step, in order, from and into ``state [slots, heads * record]``.
-    ``proj [T, ld]`` float32 holds q, k, v and the two gates' pre-activations at the columns ``offsets = (q, k, v, i, f)``."""
+    ``proj [T, ld]`` float32 holds q, k, v and the two gates' pre-activations at the columns ``offsets = (q, k, v, i, f)``.
+    ``longest``: the most tokens a request brings, or more (default: all the batch's tokens); it sizes the kernel's staging only."""
     _scan_common(proj, state, q_start, state_slot, out, heads, dv)
     if state.dim() != 2 or state.shape[1] != heads * mlstm_record(dk, dv):
         raise KernelError(f"mlstm: state {tuple(state.shape)} does not fit {heads} heads of {dk} x {dv}")
@@ -417,14 +424,14 @@ def mlstm_scan(proj: torch.Tensor, offsets, bias_i: torch.Tensor, bias_f: torch.
     if max(oq + heads * dk, ok + heads * dk, ov + heads * dv, oi + heads, of + heads) > proj.shape[1] or bias_i.shape[0] != heads or bias_f.shape[0] != heads:
         raise KernelError("mlstm: the column offsets or the biases do not fit the projection")
     _call("recurrence", "spy_mlstm_scan", _ptr(proj), ctypes.c_longlong(proj.shape[1]), oq, ok, ov, oi, of, _ptr(bias_i), _ptr(bias_f), _ptr(state),
-          state.shape[0], _ptr(q_start), _ptr(state_slot), int(num_seqs), _ptr(out), heads, dk, dv, ctypes.c_float(q_scale), ctypes.c_float(cap),
-          _ptr(status), _stream())
+          state.shape[0], _ptr(q_start), _ptr(state_slot), int(num_seqs), int(longest or proj.shape[0]), _ptr(out), heads, dk, dv,
+          ctypes.c_float(q_scale), ctypes.c_float(cap), _ptr(status), _stream())
     return out
 
 
 def delta_scan(proj: torch.Tensor, offsets, decay_pre: torch.Tensor, bias_a: torch.Tensor, decay_offset: torch.Tensor, state: torch.Tensor,
                q_start: torch.Tensor, state_slot: torch.Tensor, num_seqs: int, out: torch.Tensor, heads: int, dk: int,
-               status: Optional[torch.Tensor] = None) -> torch.Tensor:
+               status: Optional[torch.Tensor] = None, longest: Optional[int] = None) -> torch.Tensor:
     """The generalised delta rule over every request's tokens of this step, from and into ``state [slots, heads * dk * dk]``.
     ``proj [T, ld]`` float32 holds r, k, v and the removal rate's pre-activation at ``offsets = (r, k, v, a)``;
     ``decay_pre [T, heads * dk]`` the decay's pre-activation."""
@@ -439,7 +446,8 @@ def delta_scan(proj: torch.Tensor, offsets, decay_pre: torch.Tensor, bias_a: tor
     if max(o_r, ok, ov, oa) + n > proj.shape[1] or tuple(decay_pre.shape) != (proj.shape[0], n) or bias_a.shape[0] != n or decay_offset.shape[0] != n:
         raise KernelError("delta rule: the column offsets, the decay or the biases do not fit the projection")
     _call("recurrence", "spy_delta_scan", _ptr(proj), ctypes.c_longlong(proj.shape[1]), o_r, ok, ov, oa, _ptr(decay_pre), _ptr(bias_a), _ptr(decay_offset),
-          _ptr(state), state.shape[0], _ptr(q_start), _ptr(state_slot), int(num_seqs), _ptr(out), heads, dk, _ptr(status), _stream())
+          _ptr(state), state.shape[0], _ptr(q_start), _ptr(state_slot), int(num_seqs), int(longest or proj.shape[0]), _ptr(out), heads, dk,
+          _ptr(status), _stream())
     return out
 
 
@@ -528,10 +536,11 @@ def attention_mma(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Ten
 
 def attention_tc(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
                  positions: torch.Tensor, q_start: torch.Tensor, num_seqs: int, scale: float, window: Optional[int] = None,
-                 status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 status: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of a batch over its pages on tcgen05 (blocks of two 128-row query tiles that share
     every key and value tile, scores and output in tensor memory, pages brought in by TMA): prompt
-    portions, any mix.  Page sizes 8 .. 128."""
+    portions, any mix.  Page sizes 8 .. 128.  ``lse [T, nh]`` (float32, optional) receives the natural
+    logarithm of every row's sum of ``exp(score * scale)``, with which further keys can be merged in."""
     _check(q, "attention queries", torch.bfloat16, 2)
     _check(out, "attention output", torch.bfloat16, 2)
     _check(pages, "cache pages", torch.bfloat16, 5)
@@ -548,6 +557,14 @@ def attention_tc(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tens
         raise KernelError("attention: positions need one entry per token, q_start one per sequence plus one, the block table a row per sequence")
     if status is None:
         status = status_word(q.device)
+    if lse is not None:
+        _check(lse, "logarithms of the sums", torch.float32, 2)
+        if tuple(lse.shape) != (T, num_heads):
+            raise KernelError(f"attention: lse {tuple(lse.shape)} does not fit {T} tokens of {num_heads} heads")
+        _call("attention_tc", "spy_attention_tc_lse", _ptr(q), ctypes.c_longlong(q.shape[1]), _ptr(out), _ptr(lse), _ptr(pages), _ptr(block_table),
+              block_table.shape[1], page_size, num_pages, num_heads, nkv, head_dim, _ptr(positions), _ptr(q_start), T, num_seqs,
+              int(window or 0), ctypes.c_float(scale), _ptr(status), _stream())
+        return out
     _call("attention_tc", "spy_attention_tc", _ptr(q), ctypes.c_longlong(q.shape[1]), _ptr(out), _ptr(pages), _ptr(block_table),
           block_table.shape[1], page_size, num_pages, num_heads, nkv, head_dim, _ptr(positions), _ptr(q_start), T, num_seqs,
           int(window or 0), ctypes.c_float(scale), _ptr(status), _stream())

@@ -215,7 +215,7 @@ class PooledWindowAttention(Attention):
         self.o = Linear(tensors[p + n["o"]], self.ctx.dtype)
 
     def modules(self):
-        mods = ["qk_rope_store", "attention_pool"] + self.qkv.modules() + self.o.modules()
+        mods = ["qk_rope_store", "attention_pool"] + (["attention_tc"] if self.tc else []) + self.qkv.modules() + self.o.modules()
         if self.position is not None:
             mods += self.position.modules()
         return mods
@@ -241,7 +241,17 @@ class PooledWindowAttention(Attention):
             kernels.pool_store(tokens.pages, tokens.block_table, pooled.pages, pooled.block_table, self.pool, batch.positions, batch.seq_of_token,
                                status=batch.status)
         out = torch.empty((x.shape[0], self.nh * self.hd), dtype=x.dtype, device=x.device)
+        lse = None
+        if self.tc and tokens.page_size in kernels.ATTENTION_TMA_PAGE_SIZES and not batch.one_token_each:
+            # prompt portions (and whatever decodes beside them): the window's keys on the tensor cores, which also leave
+            # each row's logarithm of its sum of exponentials; the pooled entries are then merged into that softmax
+            lse = torch.empty((x.shape[0], self.nh), dtype=torch.float32, device=x.device) if self.pool else None
+            kernels.attention_tc(q, self.nh, self.hd, out, tokens.pages, tokens.block_table, batch.positions, batch.q_start, batch.num_seqs,
+                                 self.scale, window=self.window, status=batch.status, lse=lse)
+            if not self.pool:
+                return self.o(out, defer=self.defer_output)
+        # decoding batches, the float32 path and sizes the tensor-core kernel does not take: one plain kernel for both parts
         kernels.attention_pool(q, self.nh, self.hd, out, tokens.pages, tokens.block_table, pooled.pages if self.pool else None,
                                pooled.block_table if self.pool else None, batch.positions, batch.seq_of_token, self.scale, self.window, self.pool,
-                               status=batch.status)
+                               status=batch.status, lse=lse)
         return self.o(out, defer=self.defer_output)

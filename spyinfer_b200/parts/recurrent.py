@@ -93,7 +93,8 @@ class MatrixMemory(_Recurrent):
         proj = self.fused(x, out_dtype=torch.float32)
         o = torch.empty((x.shape[0], self.heads * self.dv), dtype=torch.float32, device=x.device)
         kernels.mlstm_scan(proj, self.offsets, self.bias_i, self.bias_f, cache.state, batch.q_start, batch.state_slot, batch.num_seqs, o,
-                           self.heads, self.dk, self.dv, self.dk ** -0.5, self.cap, status=batch.status)
+                           self.heads, self.dk, self.dv, self.dk ** -0.5, self.cap, status=batch.status,
+                           longest=1 if batch.one_token_each else batch.num_tokens)
         return self._finish(o, proj, self.gate_offset, self.heads, self.dv)
 
 
@@ -143,5 +144,5 @@ class DeltaRule(_Recurrent):
         decay_pre = self.w2(inner, out_dtype=torch.float32)
         o = torch.empty((x.shape[0], self.heads * self.d), dtype=torch.float32, device=x.device)
         kernels.delta_scan(proj, self.offsets, decay_pre, self.bias_a, self.decay_offset, cache.state, batch.q_start, batch.state_slot,
-                           batch.num_seqs, o, self.heads, self.d, status=batch.status)
+                           batch.num_seqs, o, self.heads, self.d, status=batch.status, longest=1 if batch.one_token_each else batch.num_tokens)
         return self._finish(o, proj, self.gate_offset, self.heads, self.d)
