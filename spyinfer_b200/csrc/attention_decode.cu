@@ -77,6 +77,7 @@ constexpr int TMEM_COLS = 64;                                    // S^T: 2 x 16 
 
 struct Params {
     bf16* out;                 // [T, nh * hd]
+    float* lse;                // null, or [T, nh]: the natural logarithm of every head's sum of exp(score) (for a caller that merges further keys in)
     const int* block_table;    // [S, table_width]
     const int* positions;      // [T]
     const int* q_start;        // [S + 1]
@@ -385,9 +386,12 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
             for (int n = 0; n < GN; ++n) sums[n] = (lred[n] + lred[NCOLS + n]) + (lred[2 * NCOLS + n] + lred[3 * NCOLS + n]);
             if (direct) {
 #pragma unroll
-                for (int n = 0; n < GN; ++n)
+                for (int n = 0; n < GN; ++n) {
                     if (n < p.G && tid < p.hd)
                         p.out[((size_t)tok * p.nh + g.kvh * p.G + n) * p.hd + tid] = __float2bfloat16_rn(sums[n] > 0.f ? __uint_as_float(o[n]) / sums[n] : 0.f);
+                    if (p.lse != nullptr && n < p.G && tid == n)
+                        p.lse[(size_t)tok * p.nh + g.kvh * p.G + n] = sums[n] > 0.f ? (m_used[n] + log2f(sums[n])) * 0.6931471805599453f : -INFINITY;
+                }
             } else {
 #pragma unroll
                 for (int n = 0; n < GN; ++n) {
@@ -452,6 +456,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
                         }
                         bf16* dst = p.out + ((size_t)tok * p.nh + g.kvh * p.G + n) * p.hd + col;
                         const float inv = L > 0.f ? 1.f / L : 0.f;
+                        if (p.lse != nullptr && col == 0) p.lse[(size_t)tok * p.nh + g.kvh * p.G + n] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
 #pragma unroll
                         for (int i = 0; i < W; i += 8) {
                             uint4 v;
@@ -628,10 +633,10 @@ extern "C" long long spy_attention_decode_scratch_floats(int seqs, int nh, int n
 // Attention of a decoding batch over its pages: every sequence brings one token (row
 // q_start[s] of q, at positions[q_start[s]]).  mode 0: the kernel decides how the work is shared
 // out; 1: the units split evenly, pairs cut where a block's share ends; 2: whole pairs.
-extern "C" int spy_attention_decode(const void* q, long long q_row_stride, void* out, const void* pages, const int* block_table, int table_width,
-                                    int page_size, int num_pages, int nh, int nkv, int hd, const int* positions, const int* q_start, int tokens,
-                                    int seqs, int window, float scale, int mode, float* scratch, long long scratch_floats, int* status,
-                                    cudaStream_t stream)
+static int run_attention_decode(const void* q, long long q_row_stride, void* out, float* lse, const void* pages, const int* block_table, int table_width,
+                                int page_size, int num_pages, int nh, int nkv, int hd, const int* positions, const int* q_start, int tokens,
+                                int seqs, int window, float scale, int mode, float* scratch, long long scratch_floats, int* status,
+                                cudaStream_t stream)
 {
     if (tokens <= 0 || seqs <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) SPY_FAIL("attention_decode: %d query heads do not group over %d key/value heads", nh, nkv);
@@ -659,7 +664,7 @@ extern "C" int spy_attention_decode(const void* q, long long q_row_stride, void*
     if (encode == nullptr) SPY_FAIL("attention_decode: cuTensorMapEncodeTiled is not available from the driver");
 
     Params p;
-    p.out = (bf16*)out; p.block_table = block_table; p.positions = positions; p.q_start = q_start; p.status = status;
+    p.out = (bf16*)out; p.lse = lse; p.block_table = block_table; p.positions = positions; p.q_start = q_start; p.status = status;
     p.part_o = scratch; p.part_ml = scratch + ((size_t)seqs * nkv + sms) * G * hd_tile;
     p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages; p.nh = nh; p.nkv = nkv; p.G = G; p.S = seqs;
     p.window = window; p.hd = hd; p.blocks = sms; p.max_keys = (int)max_keys; p.mode = mode; p.scale_log2 = scale * LOG2E;
@@ -689,4 +694,25 @@ extern "C" int spy_attention_decode(const void* q, long long q_row_stride, void*
     const int gn = G <= 4 ? 4 : (G <= 8 ? 8 : 16);
     if (hd_tile == 64) return gn == 4 ? launch<64, 4>(page_map, q_map, p, stream) : (gn == 8 ? launch<64, 8>(page_map, q_map, p, stream) : launch<64, 16>(page_map, q_map, p, stream));
     return gn == 4 ? launch<128, 4>(page_map, q_map, p, stream) : (gn == 8 ? launch<128, 8>(page_map, q_map, p, stream) : launch<128, 16>(page_map, q_map, p, stream));
+}
+
+extern "C" int spy_attention_decode(const void* q, long long q_row_stride, void* out, const void* pages, const int* block_table, int table_width,
+                                    int page_size, int num_pages, int nh, int nkv, int hd, const int* positions, const int* q_start, int tokens,
+                                    int seqs, int window, float scale, int mode, float* scratch, long long scratch_floats, int* status,
+                                    cudaStream_t stream)
+{
+    return run_attention_decode(q, q_row_stride, out, nullptr, pages, block_table, table_width, page_size, num_pages, nh, nkv, hd, positions, q_start, tokens,
+                                seqs, window, scale, mode, scratch, scratch_floats, status, stream);
+}
+
+// The same, and lse [tokens, nh] (float32) receives, for every sequence's token and head, the natural logarithm of its sum of
+// exp(score * scale): with it a caller can merge further keys into the softmax afterwards.
+extern "C" int spy_attention_decode_lse(const void* q, long long q_row_stride, void* out, float* lse, const void* pages, const int* block_table,
+                                        int table_width, int page_size, int num_pages, int nh, int nkv, int hd, const int* positions, const int* q_start,
+                                        int tokens, int seqs, int window, float scale, int mode, float* scratch, long long scratch_floats, int* status,
+                                        cudaStream_t stream)
+{
+    if (lse == nullptr) SPY_FAIL("attention_decode: no place for the logarithms of the sums");
+    return run_attention_decode(q, q_row_stride, out, lse, pages, block_table, table_width, page_size, num_pages, nh, nkv, hd, positions, q_start, tokens,
+                                seqs, window, scale, mode, scratch, scratch_floats, status, stream);
 }

@@ -39,11 +39,14 @@ template <> struct Vec4<bf16> {
 
 // ---- pooled entries ------------------------------------------------------------------------------
 // One block per (token, K or V, kv head); a token whose position ends a block of `pool` tokens writes that block's entry.
+// The block's threads form row groups: group y adds the rows y, y + groups, ... of the pooled block (so that their loads
+// are in flight together), and the groups' sums are added in the order of the groups.
 template <typename TC>
 __global__ void pool_store_kernel(const TC* __restrict__ pages, int num_pages, const int* __restrict__ block_table, TC* __restrict__ pooled,
                                   int num_pooled_pages, const int* __restrict__ pool_table, int table_width, int page_size, int nkv, int hd, int pool,
                                   const int* __restrict__ positions, const int* __restrict__ seq_of_token, int* status)
 {
+    extern __shared__ float part[];   // [groups][hd]
     pdl_enter();
     const int t = blockIdx.x, which = blockIdx.y / nkv, kvh = blockIdx.y % nkv;
     const int pos = positions[t];
@@ -53,14 +56,13 @@ __global__ void pool_store_kernel(const TC* __restrict__ pages, int num_pages, c
     const int lp_out = b / page_size;
     const int out_page = lp_out < table_width ? pool_table[(size_t)seq * table_width + lp_out] : -1;
     if (out_page < 0 || out_page >= num_pooled_pages) {
-        if (threadIdx.x == 0) report_status(status, SPY_STATUS_BAD_PAGE, t);
+        if (threadIdx.x == 0 && threadIdx.y == 0) report_status(status, SPY_STATUS_BAD_PAGE, t);
         return;
     }
-    TC* dst = pooled + ((((size_t)out_page * 2 + which) * nkv + kvh) * page_size + b % page_size) * hd;
-    const float inv = 1.0f / (float)pool;
+    const int groups = blockDim.y, y = threadIdx.y;
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float sum = 0.f;
-        for (int j = b * pool; j <= pos; ++j) {
+        for (int j = b * pool + y; j <= pos; j += groups) {
             const int lp = j / page_size;
             const int page = lp < table_width ? bt[lp] : -1;
             if (page < 0 || page >= num_pages) {
@@ -69,7 +71,17 @@ __global__ void pool_store_kernel(const TC* __restrict__ pages, int num_pages, c
             }
             sum += to_f32(pages[((((size_t)page * 2 + which) * nkv + kvh) * page_size + j % page_size) * hd + d]);
         }
-        dst[d] = from_f32<TC>(sum * inv);
+        part[y * hd + d] = sum;
+    }
+    __syncthreads();
+    if (y == 0) {
+        TC* dst = pooled + ((((size_t)out_page * 2 + which) * nkv + kvh) * page_size + b % page_size) * hd;
+        const float inv = 1.0f / (float)pool;
+        for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+            float sum = 0.f;
+            for (int g = 0; g < groups; ++g) sum += part[g * hd + d];
+            dst[d] = from_f32<TC>(sum * inv);
+        }
     }
 }
 
@@ -80,10 +92,14 @@ extern "C" int spy_pool_store(const void* pages, int num_pages, const int* block
     if (tokens <= 0) return 0;
     if (pool <= 0 || page_size <= 0 || nkv <= 0 || hd <= 0 || table_width <= 0) SPY_FAIL("pool_store: pool, page_size, heads, head size and table width must be positive");
     if (2 * nkv > 65535) SPY_FAIL("pool_store: %d key/value heads exceed the grid limit", nkv);
-    int threads = (hd + 31) / 32 * 32;
-    if (threads > 256) threads = 256;
+    int tx = (hd + 31) / 32 * 32;
+    if (tx > 128) tx = 128;
+    int ty = 256 / tx;
+    while (ty > 1 && ty > pool) ty /= 2;
+    const size_t smem = (size_t)ty * hd * sizeof(float);
+    if (smem > 48 * 1024) SPY_FAIL("pool_store: a head size of %d does not fit", hd);
     SPY_DISPATCH_DTYPE(cache_dtype, TC, {
-        spy_launch(pool_store_kernel<TC>, dim3(tokens, 2 * nkv), dim3(threads), 0, stream, (const TC*)pages, num_pages, block_table, (TC*)pooled,
+        spy_launch(pool_store_kernel<TC>, dim3(tokens, 2 * nkv), dim3(tx, ty), smem, stream, (const TC*)pages, num_pages, block_table, (TC*)pooled,
                    num_pooled_pages, pool_table, table_width, page_size, nkv, hd, pool, positions, seq_of_token, status);
     })
     SPY_CHECK_LAUNCH("pool_store");

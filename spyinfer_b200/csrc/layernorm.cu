@@ -9,13 +9,40 @@
 
 SPY_MODULE(spy_layernorm)
 
-template <typename TX, typename TD, typename TW, typename TO>
+template <typename T> struct Quad;
+template <> struct Quad<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4])
+    {
+        const float4 x = *reinterpret_cast<const float4*>(p);
+        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <> struct Quad<bf16> {
+    static __device__ __forceinline__ void load(const bf16* p, float (&v)[4])
+    {
+        const uint2 x = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&x.x), b = *reinterpret_cast<const __nv_bfloat162*>(&x.y);
+        v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float (&v)[4])
+    {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 x;
+        x.x = *reinterpret_cast<uint32_t*>(&a);
+        x.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = x;
+    }
+};
+
+// VEC: the row length is a multiple of 4 and every array is 16-byte aligned: four elements a load.
+template <typename TX, typename TD, typename TW, typename TO, bool VEC>
 __global__ void __launch_bounds__(1024)
 layernorm_kernel(TX* x, const TD* __restrict__ a, int a_splits, long long a_stride, float a_scale, const TD* __restrict__ b, int b_splits,
                  long long b_stride, float b_scale, const int* __restrict__ rows, const TW* __restrict__ w, TO* __restrict__ out, int len, float eps,
                  int write_back, int center)
 {
-    extern __shared__ float row_buf[];  // len floats, then 33 of scratch
+    extern __shared__ __align__(16) float row_buf[];  // len floats, then 33 of scratch
     pdl_enter();
     float* scratch = row_buf + len;
     const int src_row = rows ? rows[blockIdx.x] : blockIdx.x;
@@ -23,32 +50,60 @@ layernorm_kernel(TX* x, const TD* __restrict__ a, int a_splits, long long a_stri
     const TD* ar = a ? a + (size_t)src_row * len : nullptr;
     const TD* br = b ? b + (size_t)src_row * len : nullptr;
     TO* orow = out + (size_t)blockIdx.x * len;
+    constexpr int E = VEC ? 4 : 1;
     float sum = 0.f;
-    for (int i = threadIdx.x; i < len; i += blockDim.x) {
-        float v = to_f32(xr[i]);
+    for (int i = threadIdx.x * E; i < len; i += blockDim.x * E) {
+        float v[4], d[4], p[4];
+        if constexpr (VEC) Quad<TX>::load(xr + i, v); else v[0] = to_f32(xr[i]);
         if (ar) {
-            float d = 0.f;
-            for (int s = 0; s < a_splits; ++s) d += to_f32(ar[(size_t)s * a_stride + i]);
-            v = fmaf(a_scale, d, v);
+#pragma unroll
+            for (int e = 0; e < E; ++e) d[e] = 0.f;
+            for (int s = 0; s < a_splits; ++s) {
+                if constexpr (VEC) Quad<TD>::load(ar + (size_t)s * a_stride + i, p); else p[0] = to_f32(ar[(size_t)s * a_stride + i]);
+#pragma unroll
+                for (int e = 0; e < E; ++e) d[e] += p[e];
+            }
+#pragma unroll
+            for (int e = 0; e < E; ++e) v[e] = fmaf(a_scale, d[e], v[e]);
         }
         if (br) {
-            float d = 0.f;
-            for (int s = 0; s < b_splits; ++s) d += to_f32(br[(size_t)s * b_stride + i]);
-            v = fmaf(b_scale, d, v);
+#pragma unroll
+            for (int e = 0; e < E; ++e) d[e] = 0.f;
+            for (int s = 0; s < b_splits; ++s) {
+                if constexpr (VEC) Quad<TD>::load(br + (size_t)s * b_stride + i, p); else p[0] = to_f32(br[(size_t)s * b_stride + i]);
+#pragma unroll
+                for (int e = 0; e < E; ++e) d[e] += p[e];
+            }
+#pragma unroll
+            for (int e = 0; e < E; ++e) v[e] = fmaf(b_scale, d[e], v[e]);
         }
-        row_buf[i] = v;
-        sum += v;
-        if (write_back) xr[i] = from_f32<TX>(v);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            row_buf[i + e] = v[e];
+            sum += v[e];
+        }
+        if (write_back) {
+            if constexpr (VEC) Quad<TX>::store(xr + i, v); else xr[i] = from_f32<TX>(v[0]);
+        }
     }
     const float mean = center ? block_sum(sum, scratch) / (float)len : 0.f;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < len; i += blockDim.x) {
-        const float d = row_buf[i] - mean;
-        ss += d * d;
+    for (int i = threadIdx.x * E; i < len; i += blockDim.x * E) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const float dd = row_buf[i + e] - mean;
+            ss += dd * dd;
+        }
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)len + eps);
-    for (int i = threadIdx.x; i < len; i += blockDim.x) orow[i] = from_f32<TO>(((row_buf[i] - mean) * inv) * to_f32(w[i]));
+    for (int i = threadIdx.x * E; i < len; i += blockDim.x * E) {
+        float wv[4], o[4];
+        if constexpr (VEC) Quad<TW>::load(w + i, wv); else wv[0] = to_f32(w[i]);
+#pragma unroll
+        for (int e = 0; e < E; ++e) o[e] = ((row_buf[i + e] - mean) * inv) * wv[e];
+        if constexpr (VEC) Quad<TO>::store(orow + i, o); else orow[i] = from_f32<TO>(o[0]);
+    }
 }
 
 // x: [*, len] of x_dtype; a, b: null or stacks of delta_dtype; rows: null or n row indices (gather); w: [len] of w_dtype;
@@ -65,13 +120,17 @@ extern "C" int spy_layernorm(void* x, int x_dtype, const void* a, int a_splits, 
     if (!a && !b) delta_dtype = x_dtype;
     const size_t smem = (size_t)(len + 33) * sizeof(float);
     if (smem > 227 * 1024) SPY_FAIL("layernorm: a row of %d elements does not fit in shared memory (limit %d)", len, (227 * 1024) / 4 - 33);
-    int threads = (len / 4 + 31) / 32 * 32;
+    const bool vec = len % 4 == 0 && a_stride % 4 == 0 && b_stride % 4 == 0 &&
+                     ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(w) |
+                       reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    // many rows: fewer threads a row (two quads each) and so more rows an SM at a time; few rows: the row spread as wide as it goes
+    int threads = (len / (vec ? (n >= 512 ? 8 : 4) : 4) + 31) / 32 * 32;
     threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
     SPY_DISPATCH_DTYPE(x_dtype, TX, {
         SPY_DISPATCH_DTYPE(delta_dtype, TD, {
             SPY_DISPATCH_DTYPE(w_dtype, TW, {
                 SPY_DISPATCH_DTYPE(out_dtype, TO, {
-                    auto kernel = layernorm_kernel<TX, TD, TW, TO>;
+                    auto kernel = vec ? layernorm_kernel<TX, TD, TW, TO, true> : layernorm_kernel<TX, TD, TW, TO, false>;
                     if (smem > 48 * 1024) SPY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
                     spy_launch(kernel, dim3(n), dim3(threads), smem, stream, (TX*)x, (const TD*)a, a_splits, a_stride, a_scale, (const TD*)b, b_splits,
                                b_stride, b_scale, rows, (const TW*)w, (TO*)out, len, eps, write_back, center);

@@ -73,12 +73,33 @@ def count_launches(n: int) -> None:
     _launches += n
 
 
+_timed_calls = None
+
+
+def time_calls(sink) -> None:
+    """``sink`` a list: from now on every kernel call made through this module (outside stream capture) is put between
+    two CUDA events, and ``(module.function, start, end)`` is appended to the list; None turns it off.  For
+    measurements: the events keep a kernel from starting while the one before it drains, so a step runs a little
+    slower than without them."""
+    global _timed_calls
+    _timed_calls = sink
+
+
 def _call(module: str, fn: str, *args) -> None:
     global _launches
     _launches += 1
     lib = build.load(module)
     f = getattr(lib, fn)
     f.restype = ctypes.c_int
+    if _timed_calls is not None and not torch.cuda.is_current_stream_capturing():
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        rc = f(*args)
+        e1.record()
+        _timed_calls.append((f"{module}.{fn}", e0, e1))
+        if rc != 0:
+            raise KernelError(build.last_error(module))
+        return
     if f(*args) != 0:
         raise KernelError(build.last_error(module))
 
@@ -595,7 +616,7 @@ def attention_decode_takes(num_heads: int, num_kv_heads: int, head_dim: int, pag
 
 def attention_decode(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
                      positions: torch.Tensor, q_start: torch.Tensor, num_seqs: int, scale: float, window: Optional[int] = None,
-                     status: Optional[torch.Tensor] = None, share: str = "auto") -> torch.Tensor:
+                     status: Optional[torch.Tensor] = None, share: str = "auto", lse: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of a decoding batch (one token per sequence) over its pages: one persistent block
     per SM, keys in the rows of tcgen05 tiles, pages brought in by TMA, the batch's tiles shared out
     evenly over the blocks and merged through scratch memory.  At most 1024 sequences.  ``positions``,
@@ -603,7 +624,8 @@ def attention_decode(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.
     must be complete before those start (the engine copies them at the start of a step).  Launches
     on different streams must not overlap (they share the counters of the merge).  ``share``: how
     the work is dealt out, "auto" (the kernel decides), "split" (tiles split evenly, merged) or
-    "whole" ((sequence, kv head) pairs whole)."""
+    "whole" ((sequence, kv head) pairs whole).  ``lse [T, nh]`` (float32, optional) receives, at every sequence's token, the
+    natural logarithm of each head's sum of ``exp(score * scale)``, with which further keys can be merged in."""
     if share not in ("auto", "split", "whole"):
         raise KernelError(f"attention_decode: share {share!r} is not 'auto', 'split' or 'whole'")
     _check(q, "attention queries", torch.bfloat16, 2)
@@ -626,6 +648,15 @@ def attention_decode(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.
     scratch = attention_scratch(q.device, floats)
     if status is None:
         status = status_word(q.device)
+    if lse is not None:
+        _check(lse, "logarithms of the sums", torch.float32, 2)
+        if tuple(lse.shape) != (T, num_heads):
+            raise KernelError(f"attention: lse {tuple(lse.shape)} does not fit {T} tokens of {num_heads} heads")
+        _call("attention_decode", "spy_attention_decode_lse", _ptr(q), ctypes.c_longlong(q.shape[1]), _ptr(out), _ptr(lse), _ptr(pages), _ptr(block_table),
+              block_table.shape[1], page_size, num_pages, num_heads, nkv, head_dim, _ptr(positions), _ptr(q_start), T, num_seqs,
+              int(window or 0), ctypes.c_float(scale), ("auto", "split", "whole").index(share), _ptr(scratch), ctypes.c_longlong(scratch.numel()),
+              _ptr(status), _stream())
+        return out
     _call("attention_decode", "spy_attention_decode", _ptr(q), ctypes.c_longlong(q.shape[1]), _ptr(out), _ptr(pages), _ptr(block_table),
           block_table.shape[1], page_size, num_pages, num_heads, nkv, head_dim, _ptr(positions), _ptr(q_start), T, num_seqs,
           int(window or 0), ctypes.c_float(scale), ("auto", "split", "whole").index(share), _ptr(scratch), ctypes.c_longlong(scratch.numel()),

@@ -215,7 +215,7 @@ class PooledWindowAttention(Attention):
         self.o = Linear(tensors[p + n["o"]], self.ctx.dtype)
 
     def modules(self):
-        mods = ["qk_rope_store", "attention_pool"] + (["attention_tc"] if self.tc else []) + self.qkv.modules() + self.o.modules()
+        mods = ["qk_rope_store", "attention_pool"] + (["attention_tc", "attention_decode"] if self.tc else []) + self.qkv.modules() + self.o.modules()
         if self.position is not None:
             mods += self.position.modules()
         return mods
@@ -242,14 +242,25 @@ class PooledWindowAttention(Attention):
                                status=batch.status)
         out = torch.empty((x.shape[0], self.nh * self.hd), dtype=x.dtype, device=x.device)
         lse = None
-        if self.tc and tokens.page_size in kernels.ATTENTION_TMA_PAGE_SIZES and not batch.one_token_each:
-            # prompt portions (and whatever decodes beside them): the window's keys on the tensor cores, which also leave
-            # each row's logarithm of its sum of exponentials; the pooled entries are then merged into that softmax
-            lse = torch.empty((x.shape[0], self.nh), dtype=torch.float32, device=x.device) if self.pool else None
-            kernels.attention_tc(q, self.nh, self.hd, out, tokens.pages, tokens.block_table, batch.positions, batch.q_start, batch.num_seqs,
-                                 self.scale, window=self.window, status=batch.status, lse=lse)
-            if not self.pool:
-                return self.o(out, defer=self.defer_output)
+        if self.tc and tokens.page_size in kernels.ATTENTION_TMA_PAGE_SIZES:
+            # The window's keys on the tensor cores, by the kernels that attention over a plain window uses (the persistent
+            # decode kernel for requests that bring one token, the kernel for portions for the rest), which also leave each
+            # row's logarithm of its sum of exponentials; the pooled entries are then merged into that softmax.
+            decode_ok = kernels.attention_decode_takes(self.nh, self.nkv, self.hd, tokens.page_size, x.dtype)
+            fits = lambda n: 0 < n <= kernels.ATTENTION_DECODE_MAX_SEQS and n * self.nkv <= kernels.ATTENTION_DECODE_MAX_PAIRS
+            head = batch.num_seqs if batch.one_token_each else batch.one_token_head
+            if not (decode_ok and fits(head)):
+                head = 0
+            if head or not batch.one_token_each:
+                lse = torch.empty((x.shape[0], self.nh), dtype=torch.float32, device=x.device) if self.pool else None
+                if head:
+                    kernels.attention_decode(q, self.nh, self.hd, out, tokens.pages, tokens.block_table[:head], batch.positions, batch.q_start[:head + 1],
+                                             head, self.scale, window=self.window, status=batch.status, lse=lse)
+                if head < batch.num_seqs:
+                    kernels.attention_tc(q, self.nh, self.hd, out, tokens.pages, tokens.block_table[head:], batch.positions, batch.q_start[head:],
+                                         batch.num_seqs - head, self.scale, window=self.window, status=batch.status, lse=lse)
+                if not self.pool:
+                    return self.o(out, defer=self.defer_output)
         # decoding batches, the float32 path and sizes the tensor-core kernel does not take: one plain kernel for both parts
         kernels.attention_pool(q, self.nh, self.hd, out, tokens.pages, tokens.block_table, pooled.pages if self.pool else None,
                                pooled.block_table if self.pool else None, batch.positions, batch.seq_of_token, self.scale, self.window, self.pool,
