@@ -38,50 +38,56 @@ template <> struct Vec4<bf16> {
 };
 
 // ---- pooled entries ------------------------------------------------------------------------------
-// One block per (token, K or V, kv head); a token whose position ends a block of `pool` tokens writes that block's entry.
-// The block's threads form row groups: group y adds the rows y, y + groups, ... of the pooled block (so that their loads
-// are in flight together), and the groups' sums are added in the order of the groups.
+// One block per (16 tokens of the batch, K or V, kv head): it looks through its tokens, and for each whose position ends a
+// block of `pool` tokens it writes that block's entry.  The block's threads form row groups: group y adds the rows y,
+// y + groups, ... of the pooled block (so that their loads are in flight together), and the groups' sums are added in the
+// order of the groups.
+constexpr int POOL_TOKENS = 16;
+
 template <typename TC>
 __global__ void pool_store_kernel(const TC* __restrict__ pages, int num_pages, const int* __restrict__ block_table, TC* __restrict__ pooled,
                                   int num_pooled_pages, const int* __restrict__ pool_table, int table_width, int page_size, int nkv, int hd, int pool,
-                                  const int* __restrict__ positions, const int* __restrict__ seq_of_token, int* status)
+                                  const int* __restrict__ positions, const int* __restrict__ seq_of_token, int tokens, int* status)
 {
     extern __shared__ float part[];   // [groups][hd]
     pdl_enter();
-    const int t = blockIdx.x, which = blockIdx.y / nkv, kvh = blockIdx.y % nkv;
-    const int pos = positions[t];
-    if ((pos + 1) % pool != 0) return;
-    const int b = (pos + 1) / pool - 1, seq = seq_of_token[t];
-    const int* bt = block_table + (size_t)seq * table_width;
-    const int lp_out = b / page_size;
-    const int out_page = lp_out < table_width ? pool_table[(size_t)seq * table_width + lp_out] : -1;
-    if (out_page < 0 || out_page >= num_pooled_pages) {
-        if (threadIdx.x == 0 && threadIdx.y == 0) report_status(status, SPY_STATUS_BAD_PAGE, t);
-        return;
-    }
+    const int which = blockIdx.y / nkv, kvh = blockIdx.y % nkv;
     const int groups = blockDim.y, y = threadIdx.y;
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float sum = 0.f;
-        for (int j = b * pool + y; j <= pos; j += groups) {
-            const int lp = j / page_size;
-            const int page = lp < table_width ? bt[lp] : -1;
-            if (page < 0 || page >= num_pages) {
-                report_status(status, SPY_STATUS_BAD_PAGE, t);
-                continue;
-            }
-            sum += to_f32(pages[((((size_t)page * 2 + which) * nkv + kvh) * page_size + j % page_size) * hd + d]);
+    for (int t = blockIdx.x * POOL_TOKENS; t < min(tokens, (blockIdx.x + 1) * POOL_TOKENS); ++t) {
+        const int pos = positions[t];
+        if ((pos + 1) % pool != 0) continue;          // the same for every thread
+        const int b = (pos + 1) / pool - 1, seq = seq_of_token[t];
+        const int* bt = block_table + (size_t)seq * table_width;
+        const int lp_out = b / page_size;
+        const int out_page = lp_out < table_width ? pool_table[(size_t)seq * table_width + lp_out] : -1;
+        if (out_page < 0 || out_page >= num_pooled_pages) {
+            if (threadIdx.x == 0 && threadIdx.y == 0) report_status(status, SPY_STATUS_BAD_PAGE, t);
+            continue;
         }
-        part[y * hd + d] = sum;
-    }
-    __syncthreads();
-    if (y == 0) {
-        TC* dst = pooled + ((((size_t)out_page * 2 + which) * nkv + kvh) * page_size + b % page_size) * hd;
-        const float inv = 1.0f / (float)pool;
         for (int d = threadIdx.x; d < hd; d += blockDim.x) {
             float sum = 0.f;
-            for (int g = 0; g < groups; ++g) sum += part[g * hd + d];
-            dst[d] = from_f32<TC>(sum * inv);
+            for (int j = b * pool + y; j <= pos; j += groups) {
+                const int lp = j / page_size;
+                const int page = lp < table_width ? bt[lp] : -1;
+                if (page < 0 || page >= num_pages) {
+                    report_status(status, SPY_STATUS_BAD_PAGE, t);
+                    continue;
+                }
+                sum += to_f32(pages[((((size_t)page * 2 + which) * nkv + kvh) * page_size + j % page_size) * hd + d]);
+            }
+            part[y * hd + d] = sum;
         }
+        __syncthreads();
+        if (y == 0) {
+            TC* dst = pooled + ((((size_t)out_page * 2 + which) * nkv + kvh) * page_size + b % page_size) * hd;
+            const float inv = 1.0f / (float)pool;
+            for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+                float sum = 0.f;
+                for (int g = 0; g < groups; ++g) sum += part[g * hd + d];
+                dst[d] = from_f32<TC>(sum * inv);
+            }
+        }
+        __syncthreads();                              // part is rewritten for the block's next token
     }
 }
 
@@ -99,8 +105,8 @@ extern "C" int spy_pool_store(const void* pages, int num_pages, const int* block
     const size_t smem = (size_t)ty * hd * sizeof(float);
     if (smem > 48 * 1024) SPY_FAIL("pool_store: a head size of %d does not fit", hd);
     SPY_DISPATCH_DTYPE(cache_dtype, TC, {
-        spy_launch(pool_store_kernel<TC>, dim3(tokens, 2 * nkv), dim3(tx, ty), smem, stream, (const TC*)pages, num_pages, block_table, (TC*)pooled,
-                   num_pooled_pages, pool_table, table_width, page_size, nkv, hd, pool, positions, seq_of_token, status);
+        spy_launch(pool_store_kernel<TC>, dim3((tokens + POOL_TOKENS - 1) / POOL_TOKENS, 2 * nkv), dim3(tx, ty), smem, stream, (const TC*)pages, num_pages,
+                   block_table, (TC*)pooled, num_pooled_pages, pool_table, table_width, page_size, nkv, hd, pool, positions, seq_of_token, tokens, status);
     })
     SPY_CHECK_LAUNCH("pool_store");
     return 0;

@@ -24,6 +24,12 @@ constexpr int CT = 32;   // value columns a block owns
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float log_sigmoidf_(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* src)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 struct ScanArgs {
     const float* proj;      // [T, ld]
     long long ld;
@@ -32,7 +38,7 @@ struct ScanArgs {
     const float* bias1;     // mLSTM: bias of i [H];   delta: bias of the removal rate [H * dk]
     const float* bias2;     // mLSTM: bias of f [H];   delta: the decay's offset [H * dk]
     float* state;           // [slots, H, record]
-    long long record;       // floats a head: mLSTM dk * dv + (dk + 1) a column tile (padded to 4); delta dk * dv
+    long long record;       // floats a head: mLSTM dk * dv + (dk + 1) for every 8 columns (padded to 4); delta dk * dv
     int num_slots;
     const int* q_start;     // [S + 1]
     const int* state_slot;  // [S]
@@ -42,7 +48,6 @@ struct ScanArgs {
     int* status;
 };
 
-constexpr int SP = CT + 4;        // floats between the rows of a state tile while it passes through shared memory
 constexpr int THREADS = 256;      // 8 warps; warp w owns the columns 4w .. 4w + 3 of the tile, lane = 4 * (row group) + (column of the four)
 
 // A thread keeps its part of S in registers for the whole kernel: NR consecutive rows (row group rg owns the rows
@@ -54,31 +59,35 @@ constexpr int THREADS = 256;      // 8 warps; warp w owns the columns 4w .. 4w +
 // outputs are scaled and stored together.  The state enters and leaves through a tile in shared memory, so that global
 // memory is read and written in whole rows of the tile.
 // Four tokens are walked at a time: their sums over the rows are reduced together afterwards, so that the shuffles of one
-// token run beside those of the others and beside the next token's rows (nothing in S waits for them).  LIGHT: built
-// for four blocks an SM (at most 64 registers), for decoding, where a block's time is the state's way through memory.
-template <int MODE, int NR, bool LIGHT>   // MODE 0: gated matrix memory, 1: delta rule
-__global__ void __launch_bounds__(THREADS, LIGHT ? 4 : 1) scan_kernel(ScanArgs A, int TC)
+// token run beside those of the others and beside the next token's rows (nothing in S waits for them).
+// RG row groups share a warp's lanes (8, 16 or 32), so a warp owns 32 / RG columns and a block CTB = 8 * 32 / RG of them:
+// with few requests and heads the tiles are made narrow, so that there are blocks for every SM, and a thread's rows few.
+template <int MODE, int NR, int RG>   // MODE 0: gated matrix memory, 1: delta rule
+__global__ void __launch_bounds__(THREADS, NR <= 8 ? 2 : 1) scan_kernel(ScanArgs A, int TC)
 {
+    constexpr int CW = 32 / RG, CTB = 8 * CW, SPB = CTB + 4;   // columns a warp and a block own; floats between the rows of the state tile in shared memory
     extern __shared__ __align__(16) float sm[];
     pdl_enter();
-    constexpr int KS = 8 * NR;                     // floats a staged vector takes
+    constexpr int KS = RG * NR;                     // floats a staged vector takes
     constexpr int V4 = NR >= 4 ? 4 : NR;           // elements a load of a thread's rows brings
     const int dk = A.dk, dv = A.dv, H = A.H;
     float* k_s = sm;                               // [TC][KS]
     float* q_s = k_s + (size_t)TC * KS;            // [TC][KS]
     float* x1_s = q_s + (size_t)TC * KS;           // delta: removal rate [TC][KS]
     float* x2_s = x1_s + (MODE == 1 ? (size_t)TC * KS : 0);   // delta: decay [TC][KS]
-    float* v_s = x2_s + (MODE == 1 ? (size_t)TC * KS : 0);    // [TC][CT]
-    float* o_s = v_s + TC * CT;                    // [TC][CT]
-    float* g1_s = o_s + TC * CT;                   // [TC] memory: log input gate; delta: 1 / |k|
+    float* v_s = x2_s + (MODE == 1 ? (size_t)TC * KS : 0);    // [TC][CTB]
+    float* o_s = v_s + TC * CTB;                    // [TC][CTB]
+    float* g1_s = o_s + TC * CTB;                   // [TC] memory: log input gate; delta: 1 / |k|
     float* g2_s = g1_s + TC;                       // [TC] memory: log forget gate
     float* m_s = g2_s + TC;                        // [TC] memory: the running maximum after each token
     float* nqp = m_s + TC;                         // [TC][8] memory: n . q, one partial sum a warp
-    float* tile = sm;                              // [dk][SP], only before the first and after the last chunk
+    float* a_s = nqp + TC * 8;                     // [TC] memory: what a token keeps of the state, exp(f + m_before - m_after)
+    float* b_s = a_s + TC;                         // [TC] memory: what it adds, exp(i - m_after)
+    float* tile = sm;                              // [dk][SPB], only before the first and after the last chunk
 
-    const int seq = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * CT;
+    const int seq = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * CTB;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int col = warp * 4 + (lane & 3), rg = lane >> 2, r0 = rg * NR;
+    const int col = warp * CW + lane % CW, rg = lane / CW, r0 = rg * NR;
     const int t_begin = A.q_start[seq], t_end = A.q_start[seq + 1];
     if (t_begin >= t_end) return;
     const int slot = A.state_slot[seq];
@@ -87,11 +96,14 @@ __global__ void __launch_bounds__(THREADS, LIGHT ? 4 : 1) scan_kernel(ScanArgs A
         return;
     }
     float* st = A.state + ((size_t)slot * H + h) * A.record;
-    for (int idx = tid; idx < dk * CT; idx += THREADS) {
-        const int r = idx / CT, c = idx % CT;
-        tile[r * SP + c] = c0 + c < dv ? st[(size_t)r * dv + c0 + c] : 0.f;
+    for (int idx = tid; idx < dk * CTB; idx += THREADS) {
+        const int r = idx / CTB, c = idx % CTB;
+        tile[r * SPB + c] = c0 + c < dv ? st[(size_t)r * dv + c0 + c] : 0.f;
     }
-    float* st_nm = st + (size_t)dk * dv + (size_t)blockIdx.z * (dk + 1);      // this tile's own copy of n and m
+    // n and m: a copy for every 8 columns of the state (the narrowest tile); a block reads the copy of its first 8 columns and
+    // writes those of all its columns, so that every copy is the same whatever tiles the steps before and after use
+    float* st_nm = st + (size_t)dk * dv + (size_t)(c0 / 8) * (dk + 1);
+    const int copies = min(CTB / 8, (dv + 7) / 8 - c0 / 8);
     float m = 0.f, n_reg[4] = {0.f, 0.f, 0.f, 0.f};                           // n: the rows tid, tid + 256, ... (dk <= 1024)
     if (MODE == 0) {
 #pragma unroll
@@ -102,30 +114,69 @@ __global__ void __launch_bounds__(THREADS, LIGHT ? 4 : 1) scan_kernel(ScanArgs A
     __syncthreads();
     float Sr[NR];
 #pragma unroll
-    for (int i = 0; i < NR; ++i) Sr[i] = r0 + i < dk ? tile[(r0 + i) * SP + col] : 0.f;
+    for (int i = 0; i < NR; ++i) Sr[i] = r0 + i < dk ? tile[(r0 + i) * SPB + col] : 0.f;
 
+    // whether a token's vectors start on 16-byte boundaries in the projection (and in the decay's pre-activation)
+    const bool aligned = (dk & 3) == 0 && (A.ld & 3) == 0 && ((A.off_k | A.off_q) & 3) == 0 && (reinterpret_cast<uintptr_t>(A.proj) & 15) == 0 &&
+                         (MODE == 0 || ((A.off_x1 & 3) == 0 && (reinterpret_cast<uintptr_t>(A.extra) & 15) == 0));
     for (int t0 = t_begin; t0 < t_end; t0 += TC) {
         const int n_tok = min(TC, t_end - t0);
         __syncthreads();                           // the chunk before has been stored (the first time: the tile has been read)
-        for (int idx = tid; idx < n_tok * KS; idx += THREADS) {
-            const int tt = idx / KS, r = idx - tt * KS, c = h * dk + r;
-            const float* row = A.proj + (size_t)(t0 + tt) * A.ld;
-            const bool ok = r < dk;
-            k_s[idx] = ok ? row[A.off_k + c] : 0.f;
-            q_s[idx] = ok ? row[A.off_q + c] * A.q_scale : 0.f;
-            if (MODE == 1) {
-                x1_s[idx] = ok ? sigmoidf_(row[A.off_x1 + c] + A.bias1[c]) : 0.f;
-                x2_s[idx] = ok ? expf(-0.60653065971263342f * sigmoidf_(A.extra[(size_t)(t0 + tt) * H * dk + c] + A.bias2[c])) : 0.f;   // exp(-1/2) = 0.6065...
+        // The chunk's vectors come by 16-byte asynchronous copies where the columns allow it (all of them under way at once:
+        // one round trip to memory a chunk), else by plain loads; what is made of them (the scaled q, the sigmoid of the
+        // removal rate, the decay) is worked out in place afterwards.
+        if (aligned) {
+            const int quads = dk >> 2;
+            for (int idx = tid; idx < n_tok * quads; idx += THREADS) {
+                const int tt = idx / quads, qd = idx - tt * quads, c = h * dk + 4 * qd;
+                const float* row = A.proj + (size_t)(t0 + tt) * A.ld;
+                cp_async16(k_s + tt * KS + 4 * qd, row + A.off_k + c);
+                cp_async16(q_s + tt * KS + 4 * qd, row + A.off_q + c);
+                if (MODE == 1) {
+                    cp_async16(x1_s + tt * KS + 4 * qd, row + A.off_x1 + c);
+                    cp_async16(x2_s + tt * KS + 4 * qd, A.extra + (size_t)(t0 + tt) * H * dk + c);
+                }
+            }
+        } else {
+            for (int idx = tid; idx < n_tok * dk; idx += THREADS) {
+                const int tt = idx / dk, r = idx - tt * dk, c = h * dk + r;
+                const float* row = A.proj + (size_t)(t0 + tt) * A.ld;
+                k_s[tt * KS + r] = row[A.off_k + c];
+                q_s[tt * KS + r] = row[A.off_q + c];
+                if (MODE == 1) {
+                    x1_s[tt * KS + r] = row[A.off_x1 + c];
+                    x2_s[tt * KS + r] = A.extra[(size_t)(t0 + tt) * H * dk + c];
+                }
             }
         }
-        for (int idx = tid; idx < n_tok * CT; idx += THREADS) {
-            const int tt = idx / CT, c = idx % CT;
+        if (KS > dk) {
+            const int pad = KS - dk;
+            for (int idx = tid; idx < n_tok * pad; idx += THREADS) {
+                const int tt = idx / pad, r = dk + idx - tt * pad;
+                k_s[tt * KS + r] = 0.f;
+                q_s[tt * KS + r] = 0.f;
+                if (MODE == 1) { x1_s[tt * KS + r] = 0.f; x2_s[tt * KS + r] = 0.f; }
+            }
+        }
+        for (int idx = tid; idx < n_tok * CTB; idx += THREADS) {
+            const int tt = idx / CTB, c = idx % CTB;
             v_s[idx] = c0 + c < dv ? A.proj[(size_t)(t0 + tt) * A.ld + A.off_v + h * dv + c0 + c] : 0.f;
         }
         if (MODE == 0 && tid < n_tok) {
             const float* row = A.proj + (size_t)(t0 + tid) * A.ld;
             g1_s[tid] = A.cap * tanhf((row[A.off_x1 + h] + A.bias1[h]) / A.cap);
             g2_s[tid] = log_sigmoidf_(A.cap * tanhf((row[A.off_x2 + h] + A.bias2[h]) / A.cap));
+        }
+        cp_async_wait_all();
+        __syncthreads();
+        for (int idx = tid; idx < n_tok * dk; idx += THREADS) {
+            const int tt = idx / dk, r = idx - tt * dk, c = h * dk + r;
+            if (MODE == 0) {
+                q_s[tt * KS + r] *= A.q_scale;
+            } else {
+                x1_s[tt * KS + r] = sigmoidf_(x1_s[tt * KS + r] + A.bias1[c]);
+                x2_s[tt * KS + r] = expf(-0.60653065971263342f * sigmoidf_(x2_s[tt * KS + r] + A.bias2[c]));   // exp(-1/2) = 0.6065...
+            }
         }
         __syncthreads();
         if (MODE == 1) {
@@ -137,12 +188,27 @@ __global__ void __launch_bounds__(THREADS, LIGHT ? 4 : 1) scan_kernel(ScanArgs A
             }
             __syncthreads();
         }
-        // the gates of the chunk's first token; those of the token after are worked out while a token's rows are
-        float a = 1.f, b = 0.f, m_after = m;
         if (MODE == 0) {
-            m_after = fmaxf(g2_s[0] + m, g1_s[0]);
-            a = expf(g2_s[0] + m - m_after);
-            b = expf(g1_s[0] - m_after);
+            // The running maximum is a chain through the chunk's tokens (an addition and a maximum each), walked by one
+            // lane; the two exponentials of every token, which need only the maxima before and after it, are then worked
+            // out by a lane each.  The numbers are those of a token-by-token walk.
+            if (warp == 0) {
+                if (lane == 0) {
+                    float mm = m;
+                    for (int tt = 0; tt < n_tok; ++tt) {
+                        mm = fmaxf(g2_s[tt] + mm, g1_s[tt]);
+                        m_s[tt] = mm;
+                    }
+                }
+                __syncwarp();
+                for (int tt = lane; tt < n_tok; tt += 32) {
+                    const float before = tt == 0 ? m : m_s[tt - 1], after = m_s[tt];
+                    a_s[tt] = expf(g2_s[tt] + before - after);
+                    b_s[tt] = expf(g1_s[tt] - after);
+                }
+            }
+            __syncthreads();
+            m = m_s[n_tok - 1];
         }
         constexpr int U = 4;
         for (int tt0 = 0; tt0 < n_tok; tt0 += U) {
@@ -155,15 +221,10 @@ __global__ void __launch_bounds__(THREADS, LIGHT ? 4 : 1) scan_kernel(ScanArgs A
                 if (tt >= n_tok) continue;         // the same for every thread
                 const float* __restrict__ k = k_s + tt * KS + r0;
                 const float* __restrict__ q = q_s + tt * KS + r0;
-                const float v_c = v_s[tt * CT + col];
+                const float v_c = v_s[tt * CTB + col];
                 if (MODE == 0) {
-                    const float a_t = a, b_t = b;
-                    m = m_after;
-                    if (tt + 1 < n_tok) {
-                        m_after = fmaxf(g2_s[tt + 1] + m, g1_s[tt + 1]);
-                        a = expf(g2_s[tt + 1] + m - m_after);
-                        b = expf(g1_s[tt + 1] - m_after);
-                    }
+                    const float a_t = a_s[tt], b_t = b_s[tt];
+                    float part[4] = {0.f, 0.f, 0.f, 0.f};     // several short chains of sums instead of one long one
 #pragma unroll
                     for (int i0 = 0; i0 < NR; i0 += V4) {
                         float kk[V4], qq[V4];
@@ -178,9 +239,10 @@ __global__ void __launch_bounds__(THREADS, LIGHT ? 4 : 1) scan_kernel(ScanArgs A
                         for (int e = 0; e < V4; ++e) {
                             const float s = a_t * Sr[i0 + e] + (b_t * kk[e]) * v_c;
                             Sr[i0 + e] = s;
-                            acc[u] = fmaf(s, qq[e], acc[u]);
+                            part[e & 3] = fmaf(s, qq[e], part[e & 3]);
                         }
                     }
+                    acc[u] = (part[0] + part[1]) + (part[2] + part[3]);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const int r = tid + j * THREADS;
@@ -189,17 +251,17 @@ __global__ void __launch_bounds__(THREADS, LIGHT ? 4 : 1) scan_kernel(ScanArgs A
                             nq[u] += n_reg[j] * q_s[tt * KS + r];
                         }
                     }
-                    if (tid == 0) m_s[tt] = m;
                 } else {
                     const float inv = g1_s[tt];
                     const float* __restrict__ rate = x1_s + tt * KS + r0;
                     const float* __restrict__ decay = x2_s + tt * KS + r0;
-                    float us = 0.f;
+                    float part[4] = {0.f, 0.f, 0.f, 0.f};     // several short chains of sums instead of one long one
 #pragma unroll
-                    for (int i = 0; i < NR; ++i) us = fmaf(k[i] * inv, Sr[i], us);
-                    us += __shfl_xor_sync(0xffffffffu, us, 4);
-                    us += __shfl_xor_sync(0xffffffffu, us, 8);
-                    us += __shfl_xor_sync(0xffffffffu, us, 16);
+                    for (int i = 0; i < NR; ++i) part[i & 3] = fmaf(k[i] * inv, Sr[i], part[i & 3]);
+                    float us = (part[0] + part[1]) + (part[2] + part[3]);
+                    part[0] = part[1] = part[2] = part[3] = 0.f;
+#pragma unroll
+                    for (int o = CW; o <= 16; o <<= 1) us += __shfl_xor_sync(0xffffffffu, us, o);
 #pragma unroll
                     for (int i0 = 0; i0 < NR; i0 += V4) {
                         float kk[V4], qq[V4], rr[V4], dd[V4];
@@ -217,13 +279,14 @@ __global__ void __launch_bounds__(THREADS, LIGHT ? 4 : 1) scan_kernel(ScanArgs A
                             const float u_r = kk[e] * inv;
                             const float s = dd[e] * Sr[i0 + e] - (rr[e] * u_r) * us + kk[e] * v_c;
                             Sr[i0 + e] = s;
-                            acc[u] = fmaf(s, qq[e], acc[u]);
+                            part[e & 3] = fmaf(s, qq[e], part[e & 3]);
                         }
                     }
+                    acc[u] = (part[0] + part[1]) + (part[2] + part[3]);
                 }
             }
 #pragma unroll
-            for (int o = 4; o <= 16; o <<= 1) {
+            for (int o = CW; o <= 16; o <<= 1) {
 #pragma unroll
                 for (int u = 0; u < U; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o);
             }
@@ -237,14 +300,14 @@ __global__ void __launch_bounds__(THREADS, LIGHT ? 4 : 1) scan_kernel(ScanArgs A
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 if (tt0 + u < n_tok) {
-                    if (rg == 0) o_s[(tt0 + u) * CT + col] = acc[u];
+                    if (rg == 0) o_s[(tt0 + u) * CTB + col] = acc[u];
                     if (MODE == 0 && lane == 0) nqp[(tt0 + u) * 8 + warp] = nq[u];
                 }
             }
         }
         __syncthreads();
-        for (int idx = tid; idx < n_tok * CT; idx += THREADS) {
-            const int tt = idx / CT, c = idx % CT;
+        for (int idx = tid; idx < n_tok * CTB; idx += THREADS) {
+            const int tt = idx / CTB, c = idx % CTB;
             if (c0 + c >= dv) continue;
             float o = o_s[idx];
             if (MODE == 0) {
@@ -259,51 +322,200 @@ __global__ void __launch_bounds__(THREADS, LIGHT ? 4 : 1) scan_kernel(ScanArgs A
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < NR; ++i)
-        if (r0 + i < dk) tile[(r0 + i) * SP + col] = Sr[i];
+        if (r0 + i < dk) tile[(r0 + i) * SPB + col] = Sr[i];
     __syncthreads();
-    for (int idx = tid; idx < dk * CT; idx += THREADS) {
-        const int r = idx / CT, c = idx % CT;
-        if (c0 + c < dv) st[(size_t)r * dv + c0 + c] = tile[r * SP + c];
+    for (int idx = tid; idx < dk * CTB; idx += THREADS) {
+        const int r = idx / CTB, c = idx % CTB;
+        if (c0 + c < dv) st[(size_t)r * dv + c0 + c] = tile[r * SPB + c];
     }
     if (MODE == 0) {
+        for (int cp = 0; cp < copies; ++cp) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-            if (tid + j * THREADS < dk) st_nm[tid + j * THREADS] = n_reg[j];
-        if (tid == 0) st_nm[dk] = m;
+            for (int j = 0; j < 4; ++j)
+                if (tid + j * THREADS < dk) st_nm[(size_t)cp * (dk + 1) + tid + j * THREADS] = n_reg[j];
+            if (tid == 0) st_nm[(size_t)cp * (dk + 1) + dk] = m;
+        }
     }
 }
 
-template <int MODE> static int launch_scan_mode(ScanArgs& A, int num_seqs, int longest, cudaStream_t stream)
+// Decoding (every request brings one token): the state's way through memory is all there is to do, so the kernel is built
+// to keep much of it under way: a lane owns a column of the tile (a warp reads and writes whole 128-byte rows), a warp owns
+// NR consecutive rows, the loads of a thread's rows are issued before anything else, and several blocks share an SM.  Sums
+// over the rows cross the warps through shared memory.
+template <int MODE, int NR>
+__global__ void __launch_bounds__(THREADS, NR <= 16 ? 4 : 1) scan_decode_kernel(ScanArgs A)
 {
-    const int tiles = (A.dv + CT - 1) / CT;
+    __shared__ float red[8][CT], red2[8][CT], part[8], nqp[8];
+    extern __shared__ __align__(16) float vec[];      // k, q and, for the delta rule, the removal rate and the decay: dk each
+    pdl_enter();
+    const int dk = A.dk, dv = A.dv, H = A.H;
+    const int seq = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * CT;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, r0 = warp * NR;
+    const int t = A.q_start[seq];
+    if (A.q_start[seq + 1] <= t) return;
+    const int slot = A.state_slot[seq];
+    if (slot < 0 || slot >= A.num_slots) {
+        if (tid == 0) report_status(A.status, SPY_STATUS_BAD_PAGE, t);
+        return;
+    }
+    const bool col_ok = c0 + lane < dv;
+    float* st = A.state + ((size_t)slot * H + h) * A.record;
+    float Sr[NR];
+#pragma unroll
+    for (int i = 0; i < NR; ++i) Sr[i] = (r0 + i < dk && col_ok) ? st[(size_t)(r0 + i) * dv + c0 + lane] : 0.f;
+    const float* row = A.proj + (size_t)t * A.ld;
+    float *k_s = vec, *q_s = vec + dk, *x1_s = vec + 2 * dk, *x2_s = vec + 3 * dk;
+    float a = 1.f, b = 0.f, m_new = 0.f, ksq = 0.f, nq = 0.f;
+    float* st_nm = st + (size_t)dk * dv + (size_t)(c0 / 8) * (dk + 1);      // n and m: a copy for every 8 columns; the first of this tile's is read, all of them are written
+    const int copies = min(CT / 8, (dv + 7) / 8 - c0 / 8);
+    if (MODE == 0) {
+        const float ig = A.cap * tanhf((row[A.off_x1 + h] + A.bias1[h]) / A.cap);
+        const float fg = log_sigmoidf_(A.cap * tanhf((row[A.off_x2 + h] + A.bias2[h]) / A.cap));
+        const float m = st_nm[dk];
+        m_new = fmaxf(fg + m, ig);
+        a = expf(fg + m - m_new);
+        b = expf(ig - m_new);
+    }
+    for (int r = tid; r < dk; r += THREADS) {
+        const int c = h * dk + r;
+        const float kr = row[A.off_k + c], qr = row[A.off_q + c] * A.q_scale;
+        k_s[r] = kr;
+        q_s[r] = qr;
+        if (MODE == 0) {
+            const float n = a * st_nm[r] + b * kr;
+            for (int cp = 0; cp < copies; ++cp) st_nm[(size_t)cp * (dk + 1) + r] = n;
+            nq += n * qr;
+        } else {
+            x1_s[r] = sigmoidf_(row[A.off_x1 + c] + A.bias1[c]);
+            x2_s[r] = expf(-0.60653065971263342f * sigmoidf_(A.extra[(size_t)t * H * dk + c] + A.bias2[c]));
+            ksq += kr * kr;
+        }
+    }
+    if (MODE == 0) {
+        nq = warp_sum(nq);
+        if (lane == 0) nqp[warp] = nq;
+    } else {
+        ksq = warp_sum(ksq);
+        if (lane == 0) part[warp] = ksq;
+    }
+    __syncthreads();
+    const float v_c = col_ok ? row[A.off_v + h * dv + c0 + lane] : 0.f;
+    float acc = 0.f;
+    if (MODE == 0) {
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+            const int r = r0 + i;
+            if (r < dk) {
+                const float s = a * Sr[i] + (b * k_s[r]) * v_c;
+                if (col_ok) st[(size_t)r * dv + c0 + lane] = s;
+                acc = fmaf(s, q_s[r], acc);
+            }
+        }
+        red[warp][lane] = acc;
+        __syncthreads();
+        if (warp == 0 && col_ok) {
+            float o = 0.f, n = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) { o += red[w][lane]; n += nqp[w]; }
+            A.out[(size_t)t * H * dv + h * dv + c0 + lane] = o / (fmaxf(fabsf(n), expf(-m_new)) + 1e-6f);
+        }
+        if (tid == 0)
+            for (int cp = 0; cp < copies; ++cp) st_nm[(size_t)cp * (dk + 1) + dk] = m_new;
+    } else {
+        float sq = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) sq += part[w];
+        const float inv = 1.0f / sqrtf(sq + 1e-6f);
+        float us = 0.f;
+#pragma unroll
+        for (int i = 0; i < NR; ++i)
+            if (r0 + i < dk) us = fmaf(k_s[r0 + i] * inv, Sr[i], us);
+        red[warp][lane] = us;
+        __syncthreads();
+        us = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) us += red[w][lane];
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+            const int r = r0 + i;
+            if (r < dk) {
+                const float u = k_s[r] * inv;
+                const float s = x2_s[r] * Sr[i] - (x1_s[r] * u) * us + k_s[r] * v_c;
+                if (col_ok) st[(size_t)r * dv + c0 + lane] = s;
+                acc = fmaf(s, q_s[r], acc);
+            }
+        }
+        red2[warp][lane] = acc;
+        __syncthreads();
+        if (warp == 0 && col_ok) {
+            float o = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) o += red2[w][lane];
+            A.out[(size_t)t * H * dv + h * dv + c0 + lane] = o;
+        }
+    }
+}
+
+template <int MODE, int RG> static int launch_scan_rg(ScanArgs& A, int num_seqs, int longest, cudaStream_t stream)
+{
+    constexpr int CTB = 8 * (32 / RG);
+    const int tiles = (A.dv + CTB - 1) / CTB;
     int nr = 2;
-    while (8 * nr < A.dk) nr *= 2;
-    if (nr > 64) SPY_FAIL("recurrence: a key size of %d exceeds the kernel's 512", A.dk);
-    // tokens a chunk: 32, fewer when a request never brings that many (decoding) or when the vectors of 32 would not fit
+    while (RG * nr < A.dk) nr *= 2;
+    if (nr > 64) SPY_FAIL("recurrence: a key size of %d exceeds the kernel's %d", A.dk, 64 * RG);
+    // tokens a chunk: 32, fewer when a request never brings that many or when the vectors of 32 would not fit
     int tc = 32;
     while (tc > 1 && tc / 2 >= longest) tc /= 2;
     auto bytes = [&](int n) {
-        const size_t staged = ((MODE == 1 ? 4 : 2) * (size_t)n * 8 * nr + 2 * (size_t)n * CT + 11 * (size_t)n) * sizeof(float);
-        const size_t tile = (size_t)A.dk * SP * sizeof(float);
+        const size_t staged = ((MODE == 1 ? 4 : 2) * (size_t)n * RG * nr + 2 * (size_t)n * CTB + 13 * (size_t)n) * sizeof(float);
+        const size_t tile = (size_t)A.dk * (CTB + 4) * sizeof(float);
         return staged > tile ? staged : tile;
     };
     while (tc > 1 && bytes(tc) > 64 * 1024) tc /= 2;
     const size_t smem = bytes(tc);
     if (smem > 227 * 1024) SPY_FAIL("recurrence: a key size of %d does not fit a block's shared memory", A.dk);
     void (*kernel)(ScanArgs, int) = nullptr;
-    const bool light = tc == 1 && nr <= 16;   // decoding: more blocks an SM, so that more of the state is on its way at a time
     switch (nr) {
-        case 2: kernel = light ? scan_kernel<MODE, 2, true> : scan_kernel<MODE, 2, false>; break;
-        case 4: kernel = light ? scan_kernel<MODE, 4, true> : scan_kernel<MODE, 4, false>; break;
-        case 8: kernel = light ? scan_kernel<MODE, 8, true> : scan_kernel<MODE, 8, false>; break;
-        case 16: kernel = light ? scan_kernel<MODE, 16, true> : scan_kernel<MODE, 16, false>; break;
-        case 32: kernel = scan_kernel<MODE, 32, false>; break;
-        default: kernel = scan_kernel<MODE, 64, false>; break;
+        case 2: kernel = scan_kernel<MODE, 2, RG>; break;
+        case 4: kernel = scan_kernel<MODE, 4, RG>; break;
+        case 8: kernel = scan_kernel<MODE, 8, RG>; break;
+        case 16: kernel = scan_kernel<MODE, 16, RG>; break;
+        case 32: kernel = scan_kernel<MODE, 32, RG>; break;
+        default: kernel = scan_kernel<MODE, 64, RG>; break;
     }
     if (smem > 48 * 1024) SPY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     spy_launch(kernel, dim3(num_seqs, A.H, tiles), dim3(THREADS), smem, stream, A, tc);
     SPY_CHECK_LAUNCH("recurrence scan");
     return 0;
+}
+
+template <int MODE> static int launch_scan_mode(ScanArgs& A, int num_seqs, int longest, cudaStream_t stream)
+{
+    if (longest <= 1) {     // every request brings one token
+        const int tiles = (A.dv + CT - 1) / CT;
+        int nr = 2;
+        while (8 * nr < A.dk) nr *= 2;
+        if (nr > 64) SPY_FAIL("recurrence: a key size of %d exceeds the kernel's 512", A.dk);
+        void (*dk_kernel)(ScanArgs) = nullptr;
+        switch (nr) {
+            case 2: dk_kernel = scan_decode_kernel<MODE, 2>; break;
+            case 4: dk_kernel = scan_decode_kernel<MODE, 4>; break;
+            case 8: dk_kernel = scan_decode_kernel<MODE, 8>; break;
+            case 16: dk_kernel = scan_decode_kernel<MODE, 16>; break;
+            case 32: dk_kernel = scan_decode_kernel<MODE, 32>; break;
+            default: dk_kernel = scan_decode_kernel<MODE, 64>; break;
+        }
+        const size_t vec_bytes = (MODE == 1 ? 4 : 2) * (size_t)A.dk * sizeof(float);
+        spy_launch(dk_kernel, dim3(num_seqs, A.H, tiles), dim3(THREADS), vec_bytes, stream, A);
+        SPY_CHECK_LAUNCH("recurrence scan (decoding)");
+        return 0;
+    }
+    // the widest tiles (32, 16 or 8 columns a block) that still give every SM a block; key sizes above 512 need the narrower ones
+    const int sms = spy_sm_count();
+    const long long heads = (long long)num_seqs * A.H;
+    if (A.dk <= 512 && heads * ((A.dv + 31) / 32) >= sms) return launch_scan_rg<MODE, 8>(A, num_seqs, longest, stream);
+    if (A.dk <= 1024 && heads * ((A.dv + 15) / 16) >= sms) return launch_scan_rg<MODE, 16>(A, num_seqs, longest, stream);
+    return launch_scan_rg<MODE, 32>(A, num_seqs, longest, stream);
 }
 
 static int launch_scan(int mode, ScanArgs& A, int num_seqs, int longest, cudaStream_t stream)
@@ -316,7 +528,7 @@ static int launch_scan(int mode, ScanArgs& A, int num_seqs, int longest, cudaStr
 }
 
 // State record of one head, in floats.
-extern "C" long long spy_mlstm_record(int dk, int dv) { return ((long long)dk * dv + (long long)((dv + CT - 1) / CT) * (dk + 1) + 3) / 4 * 4; }
+extern "C" long long spy_mlstm_record(int dk, int dv) { return ((long long)dk * dv + (long long)((dv + 7) / 8) * (dk + 1) + 3) / 4 * 4; }
 
 extern "C" int spy_mlstm_scan(const float* proj, long long ld, int off_q, int off_k, int off_v, int off_i, int off_f, const float* bias_i, const float* bias_f,
                               float* state, int num_slots, const int* q_start, const int* state_slot, int num_seqs, int longest, float* out, int H, int dk,
@@ -338,32 +550,35 @@ extern "C" int spy_delta_scan(const float* proj, long long ld, int off_r, int of
 }
 
 // ---- what follows a recurrence: unit root mean square per head, a weight, a sigmoid gate -------------
+// One warp a (token, head) row, eight rows a block: the row's sum of squares is a sum inside the warp.
 template <typename TO>
 __global__ void gated_head_norm_kernel(const float* __restrict__ o, const float* __restrict__ proj, long long ld, int off_g, const float* __restrict__ weight,
-                                       TO* __restrict__ out, int H, int dv, float eps)
+                                       TO* __restrict__ out, long long rows, int H, int dv, float eps)
 {
-    __shared__ float scratch[33];
     pdl_enter();
-    const int t = blockIdx.x, h = blockIdx.y;
-    const float* src = o + ((size_t)t * H + h) * dv;
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const long long t = row / H;
+    const int h = (int)(row - t * H);
+    const float* src = o + row * dv;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < dv; c += blockDim.x) ss += src[c] * src[c];
-    ss = block_sum(ss, scratch);
+    for (int c = lane; c < dv; c += 32) ss += src[c] * src[c];
+    ss = warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
-    const float* g = proj + (size_t)t * ld + off_g + h * dv;
-    for (int c = threadIdx.x; c < dv; c += blockDim.x)
-        out[((size_t)t * H + h) * dv + c] = from_f32<TO>(((src[c] * inv) * weight[h * dv + c]) * sigmoidf_(g[c]));
+    const float* g = proj + t * ld + off_g + h * dv;
+    for (int c = lane; c < dv; c += 32) out[row * dv + c] = from_f32<TO>(((src[c] * inv) * weight[h * dv + c]) * sigmoidf_(g[c]));
 }
 
 extern "C" int spy_gated_head_norm(const float* o, const float* proj, long long ld, int off_g, const float* weight, void* out, int out_dtype, int tokens,
                                    int H, int dv, float eps, cudaStream_t stream)
 {
     if (tokens <= 0) return 0;
-    if (H <= 0 || dv <= 0 || H > 65535) SPY_FAIL("gated_head_norm: %d heads of %d", H, dv);
-    int threads = (dv + 31) / 32 * 32;
-    threads = threads > 256 ? 256 : (threads < 32 ? 32 : threads);
+    if (H <= 0 || dv <= 0) SPY_FAIL("gated_head_norm: %d heads of %d", H, dv);
+    const long long rows = (long long)tokens * H, blocks = (rows + 7) / 8;
+    if (blocks > 0x7fffffffLL) SPY_FAIL("gated_head_norm: %lld rows exceed the grid limit", rows);
     SPY_DISPATCH_DTYPE(out_dtype, TO, {
-        spy_launch(gated_head_norm_kernel<TO>, dim3(tokens, H), dim3(threads), 0, stream, o, proj, ld, off_g, weight, (TO*)out, H, dv, eps);
+        spy_launch(gated_head_norm_kernel<TO>, dim3((unsigned)blocks), dim3(256), 0, stream, o, proj, ld, off_g, weight, (TO*)out, rows, H, dv, eps);
     })
     SPY_CHECK_LAUNCH("gated_head_norm");
     return 0;

@@ -24,7 +24,7 @@ from .base import Mixer
 from .linear import Linear
 from .registry import register_part
 
-_TILE = 32    # value columns a block of the scan kernel owns (csrc/recurrence.cu: CT)
+_TILE = 8     # value columns of the narrowest tile of the scan kernel, each of which keeps its own n and m (csrc/recurrence.cu)
 
 
 class _Recurrent(Mixer):
