@@ -344,11 +344,29 @@ def test_pooled_window_attention_sees_exactly_its_keys(dtype, window, pool, page
         got_mean = pooled[pool_ids[b // page_size], 0, 1, b % page_size].float().cpu()
         assert torch.allclose(got_mean, k[b * pool:(b + 1) * pool, 1].mean(0), atol=1e-2 if dtype == torch.bfloat16 else 1e-6)
     out = torch.empty((T, H * d), dtype=dtype, device="cuda")
-    kernels.attention_pool(q.to(dtype).reshape(T, H * d).cuda(), H, d, out, pages, bt.cuda(), pooled, pt, positions, seq_of, 1.0, window, pool)
+    q_dev = q.to(dtype).reshape(T, H * d).cuda()
+    kernels.attention_pool(q_dev, H, d, out, pages, bt.cuda(), pooled, pt, positions, seq_of, 1.0, window, pool)
     got = out.float().cpu().view(T, H, d).double()
     tol = 3e-2 if dtype == torch.bfloat16 else 2e-5
     worst = (got - want).abs().amax(dim=(1, 2))
     assert worst.max().item() < tol, f"query {int(worst.argmax())} differs by {worst.max().item()}"
+    if dtype != torch.bfloat16 or page_size not in kernels.ATTENTION_TMA_PAGE_SIZES:
+        return
+    # The same queries on the paths that serving takes in bfloat16: the window on the tensor-core kernels, which hand out
+    # every row's log-sum-exp, and the pooled entries merged into that softmax afterwards; as one prompt ...
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    out2, lse = torch.full((T, H * d), 3.0, dtype=dtype, device="cuda"), torch.empty((T, H), dtype=torch.float32, device="cuda")
+    kernels.attention_tc(q_dev, H, d, out2, pages, bt[1:2].contiguous().cuda(), positions, i32([0, T]), 1, 1.0, window=window, lse=lse)
+    kernels.attention_pool(q_dev, H, d, out2, pages, bt.cuda(), pooled, pt, positions, seq_of, 1.0, window, pool, lse=lse)
+    worst = (out2.float().cpu().view(T, H, d).double() - want).abs().amax(dim=(1, 2))
+    assert worst.max().item() < 6e-2, f"prompt path: query {int(worst.argmax())} differs by {worst.max().item()}"
+    # ... and as T requests that each decode one token at their own position over the same pages
+    out3, lse3 = torch.full((T, H * d), 3.0, dtype=dtype, device="cuda"), torch.empty((T, H), dtype=torch.float32, device="cuda")
+    each = lambda table: table[1:2].expand(T, table.shape[1]).contiguous().cuda()
+    kernels.attention_decode(q_dev, H, d, out3, pages, each(bt), positions, i32(list(range(T + 1))), T, 1.0, window=window, lse=lse3)
+    kernels.attention_pool(q_dev, H, d, out3, pages, each(bt), pooled, each(pt.cpu()) if pool else None, positions, i32(list(range(T))), 1.0, window, pool, lse=lse3)
+    worst = (out3.float().cpu().view(T, H, d).double() - want).abs().amax(dim=(1, 2))
+    assert worst.max().item() < 6e-2, f"decode path: query {int(worst.argmax())} differs by {worst.max().item()}"
 
 
 def _state_rows(heads, record, slots):
