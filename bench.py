@@ -502,8 +502,7 @@ def nezolorn_workload(args) -> int:
         if name == "nezolorn":
             keys = sum(min(window, p + 1) for p in range(T))
             rate("kernels_prefill", "attention_tc.spy_attention_tc_lse", flops=4.0 * keys * nh * hd * n_att)
-            seen = min(window, ctx + 1) + max(0, (ctx - window + 1) // pool)
-            rate("kernels_decode_b64", "attention_pool.spy_attention_pool", nbytes=64.0 * nkv * seen * hd * 2 * 2 * n_att)
+            rate("kernels_decode_b64", "attention_decode.spy_attention_decode_lse", nbytes=64.0 * nkv * min(window, ctx + 1) * hd * 2 * 2 * n_att)
             n_mem, n_delta = n_att, layers - n_att
             mem_state = nkv * kernels.mlstm_record(hd, 2 * hd) * 4
             rate("kernels_decode_b64", "recurrence.spy_mlstm_scan", nbytes=64.0 * 2 * mem_state * n_mem)

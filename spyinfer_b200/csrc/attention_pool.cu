@@ -50,11 +50,15 @@ __global__ void pool_store_kernel(const TC* __restrict__ pages, int num_pages, c
                                   const int* __restrict__ positions, const int* __restrict__ seq_of_token, int tokens, int* status)
 {
     extern __shared__ float part[];   // [groups][hd]
+    __shared__ int pos_s[POOL_TOKENS];
     pdl_enter();
     const int which = blockIdx.y / nkv, kvh = blockIdx.y % nkv;
     const int groups = blockDim.y, y = threadIdx.y;
-    for (int t = blockIdx.x * POOL_TOKENS; t < min(tokens, (blockIdx.x + 1) * POOL_TOKENS); ++t) {
-        const int pos = positions[t];
+    const int first = blockIdx.x * POOL_TOKENS, flat = threadIdx.y * blockDim.x + threadIdx.x;
+    if (flat < POOL_TOKENS) pos_s[flat] = first + flat < tokens ? positions[first + flat] : -2;     // all at once, not one round trip a token
+    __syncthreads();
+    for (int t = first; t < min(tokens, first + POOL_TOKENS); ++t) {
+        const int pos = pos_s[t - first];
         if ((pos + 1) % pool != 0) continue;          // the same for every thread
         const int b = (pos + 1) / pool - 1, seq = seq_of_token[t];
         const int* bt = block_table + (size_t)seq * table_width;
@@ -66,14 +70,23 @@ __global__ void pool_store_kernel(const TC* __restrict__ pages, int num_pages, c
         }
         for (int d = threadIdx.x; d < hd; d += blockDim.x) {
             float sum = 0.f;
-            for (int j = b * pool + y; j <= pos; j += groups) {
-                const int lp = j / page_size;
-                const int page = lp < table_width ? bt[lp] : -1;
-                if (page < 0 || page >= num_pages) {
-                    report_status(status, SPY_STATUS_BAD_PAGE, t);
-                    continue;
+            for (int j0 = b * pool + y; j0 <= pos; j0 += 4 * groups) {      // four rows' pages are looked up, then their loads are under way together
+                const TC* src[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = j0 + e * groups;
+                    src[e] = nullptr;
+                    if (j > pos) continue;
+                    const int lp = j / page_size;
+                    const int page = lp < table_width ? bt[lp] : -1;
+                    if (page < 0 || page >= num_pages) report_status(status, SPY_STATUS_BAD_PAGE, t);
+                    else src[e] = pages + ((((size_t)page * 2 + which) * nkv + kvh) * page_size + j % page_size) * hd + d;
                 }
-                sum += to_f32(pages[((((size_t)page * 2 + which) * nkv + kvh) * page_size + j % page_size) * hd + d]);
+                float x[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) x[e] = src[e] != nullptr ? to_f32(*src[e]) : 0.f;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sum += x[e];
             }
             part[y * hd + d] = sum;
         }
@@ -98,8 +111,7 @@ extern "C" int spy_pool_store(const void* pages, int num_pages, const int* block
     if (tokens <= 0) return 0;
     if (pool <= 0 || page_size <= 0 || nkv <= 0 || hd <= 0 || table_width <= 0) SPY_FAIL("pool_store: pool, page_size, heads, head size and table width must be positive");
     if (2 * nkv > 65535) SPY_FAIL("pool_store: %d key/value heads exceed the grid limit", nkv);
-    int tx = (hd + 31) / 32 * 32;
-    if (tx > 128) tx = 128;
+    int tx = hd <= 32 ? 32 : 64;       // few threads along the head, many row groups: the rows' loads are what takes the time
     int ty = 256 / tx;
     while (ty > 1 && ty > pool) ty /= 2;
     const size_t smem = (size_t)ty * hd * sizeof(float);

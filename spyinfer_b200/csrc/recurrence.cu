@@ -192,19 +192,22 @@ __global__ void __launch_bounds__(THREADS, NR <= 8 ? 2 : 1) scan_kernel(ScanArgs
             // The running maximum is a chain through the chunk's tokens (an addition and a maximum each), walked by one
             // lane; the two exponentials of every token, which need only the maxima before and after it, are then worked
             // out by a lane each.  The numbers are those of a token-by-token walk.
-            if (warp == 0) {
-                if (lane == 0) {
-                    float mm = m;
-                    for (int tt = 0; tt < n_tok; ++tt) {
-                        mm = fmaxf(g2_s[tt] + mm, g1_s[tt]);
-                        m_s[tt] = mm;
+            if (warp == 0) {         // a chunk has at most 32 tokens: lane tt keeps token tt's gates, the chain runs through shuffles
+                const float ig = lane < n_tok ? g1_s[lane] : 0.f, fg = lane < n_tok ? g2_s[lane] : 0.f;
+                float mm = m, before = m, after = m;
+                for (int tt = 0; tt < n_tok; ++tt) {
+                    const float f_t = __shfl_sync(0xffffffffu, fg, tt), i_t = __shfl_sync(0xffffffffu, ig, tt);
+                    const float next = fmaxf(f_t + mm, i_t);
+                    if (lane == tt) {
+                        before = mm;
+                        after = next;
                     }
+                    mm = next;
                 }
-                __syncwarp();
-                for (int tt = lane; tt < n_tok; tt += 32) {
-                    const float before = tt == 0 ? m : m_s[tt - 1], after = m_s[tt];
-                    a_s[tt] = expf(g2_s[tt] + before - after);
-                    b_s[tt] = expf(g1_s[tt] - after);
+                if (lane < n_tok) {
+                    m_s[lane] = after;
+                    a_s[lane] = expf(fg + before - after);
+                    b_s[lane] = expf(ig - after);
                 }
             }
             __syncthreads();
