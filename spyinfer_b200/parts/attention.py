@@ -260,9 +260,9 @@ class PooledWindowAttention(Attention):
                     kernels.attention_tc(q, self.nh, self.hd, out, tokens.pages, tokens.block_table[head:], batch.positions, batch.q_start[head:],
                                          batch.num_seqs - head, self.scale, window=self.window, status=batch.status, lse=lse)
                 if not self.pool:
-                    return self.o(out, defer=self.defer_output)
+                    return self.o(out, defer=self.defer_output, out_dtype=self.output_dtype)
         # decoding batches, the float32 path and sizes the tensor-core kernel does not take: one plain kernel for both parts
         kernels.attention_pool(q, self.nh, self.hd, out, tokens.pages, tokens.block_table, pooled.pages if self.pool else None,
                                pooled.block_table if self.pool else None, batch.positions, batch.seq_of_token, self.scale, self.window, self.pool,
                                status=batch.status, lse=lse)
-        return self.o(out, defer=self.defer_output)
+        return self.o(out, defer=self.defer_output, out_dtype=self.output_dtype)

@@ -109,9 +109,12 @@ class Mixer(Part):
     #: residual.  A block arrangement that does anything else with the result sets this to False on
     #: the part and always gets ``[rows, size]``.
     defer_output: bool = True
+    #: None: the result has the activations' dtype; a mixer that is one of several side by side is asked for float32
+    #: here, so that the norm which adds the weighted results reads them all in one format (parts that cannot do not)
+    output_dtype: Optional[torch.dtype] = None
 
     def cache_need(self):
-        """A ``PagedCacheNeed``, a ``StateCacheNeed`` or None."""
+        """A ``PagedCacheNeed``, a ``StateCacheNeed``, a ``CompositeCacheNeed`` of them, or None."""
         return None
 
     def forward(self, x: torch.Tensor, batch, cache) -> torch.Tensor:

@@ -56,6 +56,7 @@ class ParallelMixers(Mixer):
     def forward(self, x, batch, cache):
         # each side may leave its last product unsummed only if the sum is formed by the norm behind
         self.left.defer_output = self.right.defer_output = self.defer_output and self.scaled_parts_ok
+        self.left.output_dtype = self.right.output_dtype = torch.float32 if self.scaled_parts_ok else None     # one format for the norm that adds them
         a = self.left.forward(x, batch, cache.parts[0])
         b = self.right.forward(x, batch, cache.parts[1])
         if self.scaled_parts_ok:

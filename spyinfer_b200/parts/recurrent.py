@@ -46,7 +46,7 @@ class _Recurrent(Mixer):
     def _finish(self, o, proj, gate_offset, heads, dv):
         y = torch.empty(o.shape, dtype=self.ctx.dtype, device=o.device)
         kernels.gated_head_norm(o, proj, gate_offset, self.norm_weight, y, heads, dv, self.eps)
-        return self.o(y, defer=self.defer_output)
+        return self.o(y, defer=self.defer_output, out_dtype=self.output_dtype)
 
 
 @register_part("matrix_memory")

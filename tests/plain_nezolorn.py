@@ -115,7 +115,7 @@ def left_mixer(w, pre, m, h, eps, compute, store=None):
         q, k = rotate(q, pos, m["rot"], compute), rotate(k, pos, m["rot"], compute)
     if store is not None:                    # what a cache in a narrower format would hold
         k, v = store(k), store(v)
-    o = windowed_pooled_attention(q, k, v, m["mask"]["size"], m["mask"]["pool"], m["scale"])
+    o = windowed_pooled_attention(q, k, v, m["mask"]["size"], m["mask"].get("pool") or 10 ** 9, m["scale"])     # no pool: no block is ever complete
     return lin(o.reshape(T, -1), w[pre + "o"])
 
 

@@ -20,7 +20,9 @@ gpu = pytest.mark.gpu
 # band scaling, values wider than keys in the memory, a layer without feed-forward; b has no pair table, as many
 # key/value heads as heads, band scaling with a short original length (all three bands occur), a pool of one token and a
 # pool longer than its window, a decay rank that is no multiple of 8; c has head sizes that the tensor-core products
-# take, two column tiles in the memory's state, and grouped heads.
+# take, two column tiles in the memory's state, and grouped heads; d has delta-rule layers only (no pages at all), one of
+# them without a feed-forward, and a width that is no multiple of 16; e has attention without rotation and without
+# pooled blocks, and a head size that is no multiple of 8.
 NZ = {
     "a": dict(seed=5, config={
         "architecture": "Nezolorn", "vocab": 211, "width": 64, "residual_mult": 0.5, "norm": {"eps": 1e-5},
@@ -64,6 +66,22 @@ NZ = {
                                 "rot": {"base": 50000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 512}}},
                        "right": {"heads": 4, "dim": 32, "vdim": 64, "gate_cap": 12.0}}},
             {"type": "general_delta", "mlp": {"kind": "dense", "ff": 160}, "mixer": {"heads": 2, "dim": 64, "decay_rank": 16}},
+        ]}),
+    "d": dict(seed=8, config={
+        "architecture": "Nezolorn", "vocab": 157, "width": 40, "residual_mult": 0.8, "norm": {"eps": 1e-5},
+        "embedding": {"scale": 2.0, "bigram": {"buckets": 31, "mul_prev": 1, "mul_cur": 1}},
+        "layers": [
+            {"type": "general_delta", "mlp": None, "mixer": {"heads": 1, "dim": 24, "decay_rank": 3}},
+            {"type": "general_delta", "mlp": {"kind": "dense", "ff": 56}, "mixer": {"heads": 5, "dim": 8, "decay_rank": 8}},
+        ]}),
+    "e": dict(seed=9, config={
+        "architecture": "Nezolorn", "vocab": 97, "width": 48, "residual_mult": 1.0, "norm": {"eps": 1e-6},
+        "embedding": {"scale": 1.0},
+        "layers": [
+            {"type": "parallel", "mlp": {"kind": "dense", "ff": 72},
+             "mixer": {"left_scale": 1.0, "right_scale": 1.0,
+                       "left": {"heads": 3, "kv_heads": 3, "dim": 12, "vdim": 12, "scale": 0.4, "mask": {"size": 25}},
+                       "right": {"heads": 1, "dim": 12, "vdim": 20, "gate_cap": 10.0}}},
         ]}),
 }
 TOL = {"float32": 2e-4, "bfloat16": 6e-2}      # largest difference over the largest logit
