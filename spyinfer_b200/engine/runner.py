@@ -90,7 +90,7 @@ class ModelRunner:
     def _pages_from_free_memory(self, needs) -> int:
         """The pool size that the free device memory allows: windowed groups take what their windows
         need (``CacheManager.pages_of_group``), the rest goes to the groups that keep every key."""
-        from ..config.spec import CompositeCacheNeed, PagedCacheNeed
+        from ..config.spec import CompositeCacheNeed, PagedCacheNeed, StateCacheNeed
         needs = [m for n in needs for m in (n.flat() if isinstance(n, CompositeCacheNeed) else [n])]
         cfg = self.config
         page, step = cfg.kvcache_block_size, max(cfg.max_num_batched_tokens, cfg.max_num_seqs)
@@ -102,8 +102,16 @@ class ModelRunner:
         elt = torch.empty((), dtype=self.model.ctx.dtype).element_size()
         fixed = sum(CacheManager.pages_of_group(n.window, page, 1 << 30, cfg.max_num_seqs, step) * 2 * n.num_kv_heads * page * n.head_dim * elt
                     for n in windowed)
+        # the per-request states of recurrent parts (one row a slot and the spare one) are allocated beside the pages
+        states = 0
+        for n in needs:
+            if isinstance(n, StateCacheNeed):
+                size = torch.empty((), dtype=getattr(torch, n.dtype)).element_size()
+                for d in n.shape:
+                    size *= int(d)
+                states += (cfg.max_num_seqs + 1) * size
         free, total = torch.cuda.mem_get_info(self.device)
-        budget = free - int(total * (1.0 - cfg.gpu_memory_utilization)) - (2 << 30) - fixed  # room for activations
+        budget = free - int(total * (1.0 - cfg.gpu_memory_utilization)) - (2 << 30) - fixed - states  # room for activations
         pages = budget // per_page
         most = cfg.max_num_seqs * ((cfg.max_model_len + page - 1) // page)
         if pages <= 0:
