@@ -123,6 +123,23 @@ static inline void spy_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     if (e != cudaSuccess) g_spy_launch_error = e;
 }
 
+// A launch in plain stream order (no programmatic dependent launch: the kernel's blocks are placed only once the kernel
+// before it has ended).  For kernels that run long on about one block an SM: started early, their blocks pile up on the
+// SMs that the kernel ahead leaves first and stay there.
+template <typename... KArgs, typename... Args>
+static inline void spy_launch_in_order(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = nullptr;
+    cfg.numAttrs = 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) g_spy_launch_error = e;
+}
+
 // The same for a kernel whose blocks form clusters of `cluster` along x.
 template <typename... KArgs, typename... Args>
 static inline void spy_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, unsigned cluster, Args... args)

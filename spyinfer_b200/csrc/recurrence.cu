@@ -28,6 +28,10 @@ __device__ __forceinline__ void cp_async16(float* smem_dst, const float* src)
 {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async4(float* smem_dst, const float* src)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 struct ScanArgs {
@@ -67,19 +71,16 @@ __global__ void __launch_bounds__(THREADS, NR <= 8 ? 2 : 1) scan_kernel(ScanArgs
 {
     constexpr int CW = 32 / RG, CTB = 8 * CW, SPB = CTB + 4;   // columns a warp and a block own; floats between the rows of the state tile in shared memory
     extern __shared__ __align__(16) float sm[];
-    pdl_enter();
+    // Launched in plain stream order (spy_launch_in_order): it runs long on about a block an SM, and started early its
+    // blocks piled up on the SMs that the product ahead left first (a prompt step was a sixth slower).
+    pdl_wait();
     constexpr int KS = RG * NR;                     // floats a staged vector takes
     constexpr int V4 = NR >= 4 ? 4 : NR;           // elements a load of a thread's rows brings
     const int dk = A.dk, dv = A.dv, H = A.H;
-    float* k_s = sm;                               // [TC][KS]
-    float* q_s = k_s + (size_t)TC * KS;            // [TC][KS]
-    float* x1_s = q_s + (size_t)TC * KS;           // delta: removal rate [TC][KS]
-    float* x2_s = x1_s + (MODE == 1 ? (size_t)TC * KS : 0);   // delta: decay [TC][KS]
-    float* v_s = x2_s + (MODE == 1 ? (size_t)TC * KS : 0);    // [TC][CTB]
-    float* o_s = v_s + TC * CTB;                    // [TC][CTB]
-    float* g1_s = o_s + TC * CTB;                   // [TC] memory: log input gate; delta: 1 / |k|
-    float* g2_s = g1_s + TC;                       // [TC] memory: log forget gate
-    float* m_s = g2_s + TC;                        // [TC] memory: the running maximum after each token
+    // two stages of a chunk's vectors (the next chunk's arrive while this one's tokens are walked), then what a chunk makes
+    const size_t stage_floats = (size_t)(MODE == 1 ? 4 : 2) * TC * KS + (size_t)TC * CTB + 2 * (size_t)TC;
+    float* o_s = sm + 2 * stage_floats;            // [TC][CTB]
+    float* m_s = o_s + TC * CTB;                   // [TC] memory: the running maximum after each token
     float* nqp = m_s + TC;                         // [TC][8] memory: n . q, one partial sum a warp
     float* a_s = nqp + TC * 8;                     // [TC] memory: what a token keeps of the state, exp(f + m_before - m_after)
     float* b_s = a_s + TC;                         // [TC] memory: what it adds, exp(i - m_after)
@@ -119,12 +120,18 @@ __global__ void __launch_bounds__(THREADS, NR <= 8 ? 2 : 1) scan_kernel(ScanArgs
     // whether a token's vectors start on 16-byte boundaries in the projection (and in the decay's pre-activation)
     const bool aligned = (dk & 3) == 0 && (A.ld & 3) == 0 && ((A.off_k | A.off_q) & 3) == 0 && (reinterpret_cast<uintptr_t>(A.proj) & 15) == 0 &&
                          (MODE == 0 || ((A.off_x1 & 3) == 0 && (reinterpret_cast<uintptr_t>(A.extra) & 15) == 0));
-    for (int t0 = t_begin; t0 < t_end; t0 += TC) {
+    // Requests a chunk's vectors into a stage: 16-byte asynchronous copies where the columns allow it (all under way at once),
+    // else plain loads; v and the gates' pre-activations by 4-byte copies.  What is made of them (the scaled q, the sigmoid of
+    // the removal rate, the decay, the capped gates) is worked out in place once they have landed.
+    auto request = [&](int t0, int stage) {
         const int n_tok = min(TC, t_end - t0);
-        __syncthreads();                           // the chunk before has been stored (the first time: the tile has been read)
-        // The chunk's vectors come by 16-byte asynchronous copies where the columns allow it (all of them under way at once:
-        // one round trip to memory a chunk), else by plain loads; what is made of them (the scaled q, the sigmoid of the
-        // removal rate, the decay) is worked out in place afterwards.
+        float* k_s = sm + stage * stage_floats;
+        float* q_s = k_s + (size_t)TC * KS;
+        float* x1_s = q_s + (size_t)TC * KS;
+        float* x2_s = x1_s + (MODE == 1 ? (size_t)TC * KS : 0);
+        float* v_s = x2_s + (MODE == 1 ? (size_t)TC * KS : 0);
+        float* g1_s = v_s + TC * CTB;
+        float* g2_s = g1_s + TC;
         if (aligned) {
             const int quads = dk >> 2;
             for (int idx = tid; idx < n_tok * quads; idx += THREADS) {
@@ -141,11 +148,11 @@ __global__ void __launch_bounds__(THREADS, NR <= 8 ? 2 : 1) scan_kernel(ScanArgs
             for (int idx = tid; idx < n_tok * dk; idx += THREADS) {
                 const int tt = idx / dk, r = idx - tt * dk, c = h * dk + r;
                 const float* row = A.proj + (size_t)(t0 + tt) * A.ld;
-                k_s[tt * KS + r] = row[A.off_k + c];
-                q_s[tt * KS + r] = row[A.off_q + c];
+                cp_async4(k_s + tt * KS + r, row + A.off_k + c);
+                cp_async4(q_s + tt * KS + r, row + A.off_q + c);
                 if (MODE == 1) {
-                    x1_s[tt * KS + r] = row[A.off_x1 + c];
-                    x2_s[tt * KS + r] = A.extra[(size_t)(t0 + tt) * H * dk + c];
+                    cp_async4(x1_s + tt * KS + r, row + A.off_x1 + c);
+                    cp_async4(x2_s + tt * KS + r, A.extra + (size_t)(t0 + tt) * H * dk + c);
                 }
             }
         }
@@ -160,15 +167,29 @@ __global__ void __launch_bounds__(THREADS, NR <= 8 ? 2 : 1) scan_kernel(ScanArgs
         }
         for (int idx = tid; idx < n_tok * CTB; idx += THREADS) {
             const int tt = idx / CTB, c = idx % CTB;
-            v_s[idx] = c0 + c < dv ? A.proj[(size_t)(t0 + tt) * A.ld + A.off_v + h * dv + c0 + c] : 0.f;
+            if (c0 + c < dv) cp_async4(v_s + idx, A.proj + (size_t)(t0 + tt) * A.ld + A.off_v + h * dv + c0 + c);
+            else v_s[idx] = 0.f;
         }
         if (MODE == 0 && tid < n_tok) {
             const float* row = A.proj + (size_t)(t0 + tid) * A.ld;
-            g1_s[tid] = A.cap * tanhf((row[A.off_x1 + h] + A.bias1[h]) / A.cap);
-            g2_s[tid] = log_sigmoidf_(A.cap * tanhf((row[A.off_x2 + h] + A.bias2[h]) / A.cap));
+            cp_async4(g1_s + tid, row + A.off_x1 + h);
+            cp_async4(g2_s + tid, row + A.off_x2 + h);
         }
+    };
+    __syncthreads();                               // the tile has been read: its place is the stages' now
+    request(t_begin, 0);
+    int stage = 0;
+    for (int t0 = t_begin; t0 < t_end; t0 += TC, stage ^= 1) {
+        const int n_tok = min(TC, t_end - t0);
+        float* k_s = sm + stage * stage_floats;
+        float* q_s = k_s + (size_t)TC * KS;
+        float* x1_s = q_s + (size_t)TC * KS;
+        float* x2_s = x1_s + (MODE == 1 ? (size_t)TC * KS : 0);
+        float* v_s = x2_s + (MODE == 1 ? (size_t)TC * KS : 0);
+        float* g1_s = v_s + TC * CTB;
+        float* g2_s = g1_s + TC;
         cp_async_wait_all();
-        __syncthreads();
+        __syncthreads();                           // this chunk's vectors have landed; the chunk before has been stored
         for (int idx = tid; idx < n_tok * dk; idx += THREADS) {
             const int tt = idx / dk, r = idx - tt * dk, c = h * dk + r;
             if (MODE == 0) {
@@ -177,6 +198,10 @@ __global__ void __launch_bounds__(THREADS, NR <= 8 ? 2 : 1) scan_kernel(ScanArgs
                 x1_s[tt * KS + r] = sigmoidf_(x1_s[tt * KS + r] + A.bias1[c]);
                 x2_s[tt * KS + r] = expf(-0.60653065971263342f * sigmoidf_(x2_s[tt * KS + r] + A.bias2[c]));   // exp(-1/2) = 0.6065...
             }
+        }
+        if (MODE == 0 && tid < n_tok) {
+            g1_s[tid] = A.cap * tanhf((g1_s[tid] + A.bias1[h]) / A.cap);
+            g2_s[tid] = log_sigmoidf_(A.cap * tanhf((g2_s[tid] + A.bias2[h]) / A.cap));
         }
         __syncthreads();
         if (MODE == 1) {
@@ -213,6 +238,7 @@ __global__ void __launch_bounds__(THREADS, NR <= 8 ? 2 : 1) scan_kernel(ScanArgs
             __syncthreads();
             m = m_s[n_tok - 1];
         }
+        if (t0 + TC < t_end) request(t0 + TC, stage ^ 1);     // the stage that the chunk before used; every thread is past that chunk
         constexpr int U = 4;
         for (int tt0 = 0; tt0 < n_tok; tt0 += U) {
             float acc[U], nq[U];
@@ -339,6 +365,7 @@ __global__ void __launch_bounds__(THREADS, NR <= 8 ? 2 : 1) scan_kernel(ScanArgs
             if (tid == 0) st_nm[(size_t)cp * (dk + 1) + dk] = m;
         }
     }
+    pdl_launch_dependents();
 }
 
 // Decoding (every request brings one token): the state's way through memory is all there is to do, so the kernel is built
@@ -470,11 +497,12 @@ template <int MODE, int RG> static int launch_scan_rg(ScanArgs& A, int num_seqs,
     int tc = 32;
     while (tc > 1 && tc / 2 >= longest) tc /= 2;
     auto bytes = [&](int n) {
-        const size_t staged = ((MODE == 1 ? 4 : 2) * (size_t)n * RG * nr + 2 * (size_t)n * CTB + 13 * (size_t)n) * sizeof(float);
+        const size_t stage = (MODE == 1 ? 4 : 2) * (size_t)n * RG * nr + (size_t)n * CTB + 2 * (size_t)n;      // one stage of a chunk's vectors
+        const size_t staged = (2 * stage + (size_t)n * CTB + 11 * (size_t)n) * sizeof(float);
         const size_t tile = (size_t)A.dk * (CTB + 4) * sizeof(float);
         return staged > tile ? staged : tile;
     };
-    while (tc > 1 && bytes(tc) > 64 * 1024) tc /= 2;
+    while (tc > 1 && bytes(tc) > 100 * 1024) tc /= 2;
     const size_t smem = bytes(tc);
     if (smem > 227 * 1024) SPY_FAIL("recurrence: a key size of %d does not fit a block's shared memory", A.dk);
     void (*kernel)(ScanArgs, int) = nullptr;
@@ -487,7 +515,7 @@ template <int MODE, int RG> static int launch_scan_rg(ScanArgs& A, int num_seqs,
         default: kernel = scan_kernel<MODE, 64, RG>; break;
     }
     if (smem > 48 * 1024) SPY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    spy_launch(kernel, dim3(num_seqs, A.H, tiles), dim3(THREADS), smem, stream, A, tc);
+    spy_launch_in_order(kernel, dim3(num_seqs, A.H, tiles), dim3(THREADS), smem, stream, A, tc);
     SPY_CHECK_LAUNCH("recurrence scan");
     return 0;
 }
@@ -513,11 +541,20 @@ template <int MODE> static int launch_scan_mode(ScanArgs& A, int num_seqs, int l
         SPY_CHECK_LAUNCH("recurrence scan (decoding)");
         return 0;
     }
-    // the widest tiles (32, 16 or 8 columns a block) that still give every SM a block; key sizes above 512 need the narrower ones
+    // the widest tiles (32, 16 or 8 columns a block) that still give (nearly) every SM a block; key sizes above 512 need the narrower ones
     const int sms = spy_sm_count();
     const long long heads = (long long)num_seqs * A.H;
+    static int forced = -1;                      // SPYINFER_SCAN_RG = 8, 16 or 32 in the environment fixes the tile width (for measurements)
+    if (forced < 0) {
+        const char* e = getenv("SPYINFER_SCAN_RG");
+        forced = e != nullptr ? atoi(e) : 0;
+    }
+    if (forced == 8 && A.dk <= 512) return launch_scan_rg<MODE, 8>(A, num_seqs, longest, stream);
+    if (forced == 16 && A.dk <= 1024) return launch_scan_rg<MODE, 16>(A, num_seqs, longest, stream);
+    if (forced == 32) return launch_scan_rg<MODE, 32>(A, num_seqs, longest, stream);
+    // measured on one request of 8 heads, 128 x 256: 64 blocks of 32 columns 0.79 ms, 128 of 16 columns 0.64, 256 of 8 columns 0.75
     if (A.dk <= 512 && heads * ((A.dv + 31) / 32) >= sms) return launch_scan_rg<MODE, 8>(A, num_seqs, longest, stream);
-    if (A.dk <= 1024 && heads * ((A.dv + 15) / 16) >= sms) return launch_scan_rg<MODE, 16>(A, num_seqs, longest, stream);
+    if (A.dk <= 1024 && 4 * heads * ((A.dv + 15) / 16) >= 3 * sms) return launch_scan_rg<MODE, 16>(A, num_seqs, longest, stream);
     return launch_scan_rg<MODE, 32>(A, num_seqs, longest, stream);
 }
 
