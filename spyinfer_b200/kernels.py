@@ -435,7 +435,8 @@ def mlstm_scan(proj: torch.Tensor, offsets, bias_i: torch.Tensor, bias_f: torch.
                status: Optional[torch.Tensor] = None, longest: Optional[int] = None) -> torch.Tensor:
     """The gated matrix memory over every request's tokens of this step, in order, from and into ``state [slots, heads * record]``.
     ``proj [T, ld]`` float32 holds q, k, v and the two gates' pre-activations at the columns ``offsets = (q, k, v, i, f)``.
-    ``longest``: the most tokens a request brings, or more (default: all the batch's tokens); it sizes the kernel's staging only."""
+    ``longest``: the most tokens a request brings, or more (default: all the batch's tokens): it sizes the kernel's staging, and 1
+    says that every request brings exactly one token (the kernel made for decoding then runs; ``delta_scan`` likewise)."""
     _scan_common(proj, state, q_start, state_slot, out, heads, dv)
     if state.dim() != 2 or state.shape[1] != heads * mlstm_record(dk, dv):
         raise KernelError(f"mlstm: state {tuple(state.shape)} does not fit {heads} heads of {dk} x {dv}")
