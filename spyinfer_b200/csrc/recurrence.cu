@@ -6,20 +6,20 @@
 //                                            both terms reading the old S, w a decay and r a removal rate per key channel;
 // and what follows both: each head's output divided by its root mean square, times a weight, times a sigmoid gate.
 //
-// One kernel serves prompt portions and decoding: a block owns CT = 32 value columns of one (request, head), holds its
-// [dk x 32] tile of S in shared memory and walks the request's tokens of this step in order (`longest`: the most tokens a
-// request of the step brings, or more; it only sizes the chunks that are staged in shared memory).  The columns of S do not
-// depend on one another, so the tiles of a head run side by side; the vector n and the maximum m, which all tiles of a head
-// need, are kept and updated by each tile for itself (dk + 1 numbers a tile in the state record: no tile ever reads what
-// another writes, whenever their blocks happen to run).  The per-token arithmetic is the same
-// whatever the step's cut, so a position's result does not depend on how its request was cut into steps.
+// A block owns a tile of value columns of one (request, head) (32, 16 or 8 of them: whatever gives the SMs a block each) and
+// walks the request's tokens of this step in order, with its part of S in registers.  The columns of S do not depend on one
+// another, so the tiles of a head run side by side; the vector n and the maximum m, which all tiles of a head need, are
+// kept and updated by each tile for itself (dk + 1 numbers for every 8 columns in the state record: no tile ever reads
+// what another writes, whenever their blocks happen to run).  Two kernels: one for steps with prompt portions (scan_kernel),
+// whose arithmetic for a token does not depend on where a portion starts or ends, and one for steps in which every request
+// brings one token (scan_decode_kernel: `longest` = 1), whose sums over a column's rows run in another order.
 //
 // Inputs are columns of one 32-bit activation matrix `proj` [T, ld] (the fused projection of the mixer's input).
 #include "common.cuh"
 
 SPY_MODULE(spy_recurrence)
 
-constexpr int CT = 32;   // value columns a block owns
+constexpr int CT = 32;   // value columns a block of the decode kernel owns, and the widest tile of the other
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float log_sigmoidf_(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
