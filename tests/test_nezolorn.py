@@ -564,6 +564,35 @@ def test_unequal_batches_with_pages_and_slots_used_again(models, name, dtype):
 
 
 @gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "c"])
+def test_four_decoding_requests_beside_a_prompt_portion(models, name, dtype):
+    """From four one-token requests on, a mixed step lays them out first and their attention takes the kernel made for
+    decoding while the portion beside them takes the one for portions; every row still equals the plain model's."""
+    from spyinfer_b200.engine.batch import StepEntry
+
+    runner = make_runner(models[name][0], dtype, page_size=16, num_pages=60, max_num_seqs=5)
+    olds = {f"o{n}": tokens_of(name, n, salt=5) for n in (70, 90, 33, 120)}
+    new = tokens_of(name, 150, salt=6)
+    for rid, toks in olds.items():                       # all but the last ten tokens of each
+        runner.step([StepEntry(rid, toks[:-10], [])])
+    worst, at = 0.0, 0
+    for k, n in enumerate((37, 2, 41, 16, 3, 20, 5, 9, 11, 6)):
+        entries = [StepEntry("new", new[at:at + n], list(range(n)))]
+        entries[1:1] = [StepEntry(rid, [toks[len(toks) - 10 + k]], [0]) for rid, toks in olds.items()]     # the portion first, then the four
+        logits = runner.step(entries).float().cpu().numpy()
+        want_new = plain_logits(name, models, new)
+        scale = np.abs(want_new).max()
+        worst = max(worst, float(np.abs(logits[:n] - want_new[at:at + n]).max() / scale))
+        for j, (rid, toks) in enumerate(olds.items()):
+            want = plain_logits(name, models, toks)
+            worst = max(worst, float(np.abs(logits[n + j] - want[len(toks) - 10 + k]).max() / np.abs(want).max()))
+        at += n
+    runner.check_status()
+    assert at == len(new) and worst < TOL[dtype]
+
+
+@gpu
 def test_the_replay_program_runs_the_model(models, tmp_path):
     name = "a"
     rng = random.Random(2)
