@@ -239,7 +239,7 @@ __global__ void __launch_bounds__(THREADS, NR <= 8 ? 2 : 1) scan_kernel(ScanArgs
             m = m_s[n_tok - 1];
         }
         if (t0 + TC < t_end) request(t0 + TC, stage ^ 1);     // the stage that the chunk before used; every thread is past that chunk
-        constexpr int U = 4;
+        constexpr int U = NR <= 8 ? 8 : 4;         // tokens walked at a time (their reductions run together); fewer when a thread's rows take many registers
         for (int tt0 = 0; tt0 < n_tok; tt0 += U) {
             float acc[U], nq[U];
 #pragma unroll
