@@ -4,7 +4,7 @@ what the layers need, and slots for per-request state of fixed size.
 * Every entry of the model's run order that owns a cache declares its need.  Entries with
   equal paged needs (same heads, head size and window) form a *group*: one pool of page
   ids, one block table per request, one device tensor
-  ``[entries, pages, 2 (K, V), kv_heads, page_size, head_dim]``.  A page id addresses the
+  ``[entries, pages, planes (K, V; or K alone), kv_heads, page_size, head_dim]``.  A page id addresses the
   same token range in every entry of its group.
 * A request holds, per group, the pages of the positions it has stored.  In a windowed group
   the pages that lie wholly behind the window of every future query are given back when a
@@ -44,7 +44,7 @@ class CacheView:
 
     kind: str                      # "paged", "state", "composite" or "none"
     group: int = -1
-    pages: Optional[torch.Tensor] = None        # [pages, 2, kv_heads, page_size, head_dim] of this entry
+    pages: Optional[torch.Tensor] = None        # [pages, planes, kv_heads, page_size, head_dim] of this entry
     block_table: Optional[torch.Tensor] = None  # [S, width] int32 on the device, set for each step
     page_size: int = 0
     window: Optional[int] = None
@@ -146,7 +146,7 @@ class CacheManager:
                 n = g.need
                 # one page more than the pool hands out: the spare page (the id after the pool's last) takes
                 # the writes of the padding rows of a fixed-size (captured) decode batch
-                g.pages = torch.zeros((len(g.entries), pool_pages + 1, 2, n.num_kv_heads, page_size, n.head_dim), dtype=dtype, device=device)
+                g.pages = torch.zeros((len(g.entries), pool_pages + 1, n.planes, n.num_kv_heads, page_size, n.head_dim), dtype=dtype, device=device)
         for v, k in self._paged:
             if self.groups[v.group].pages is not None:
                 v.pages = self.groups[v.group].pages[k]
@@ -199,7 +199,7 @@ class CacheManager:
         flat = [m for n in needs for m in (n.flat() if isinstance(n, CompositeCacheNeed) else [n])]
         paged = [n for n in flat if isinstance(n, PagedCacheNeed)]
         full = [n for n in paged if n.window is None] or paged
-        return sum(-(-2 * n.num_kv_heads * page_size * n.head_dim * elt // n.stride) for n in full)
+        return sum(-(-n.planes * n.num_kv_heads * page_size * n.head_dim * elt // n.stride) for n in full)
 
     def most_tokens_alone(self) -> int:
         """The most tokens of ONE request that the pools can hold (beyond ``max_model_len`` if only

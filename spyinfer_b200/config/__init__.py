@@ -5,9 +5,11 @@ from .model_config import (ArchitectureConfig, ConfigError, config_from_json, kn
 from .spec import CompositeCacheNeed, LayerSpec, ModelSpec, PagedCacheNeed, PartSpec, RunEntry, StateCacheNeed
 from . import qwen3 as _qwen3  # registers "Qwen3ForCausalLM"
 from . import nezolorn as _nezolorn  # registers "Nezolorn"
+from . import daronex as _daronex  # registers "Daronex"
+from .daronex import DaronexConfig
 from .nezolorn import NezolornConfig
 from .qwen3 import Qwen3Config
 
 __all__ = ["EngineConfig", "ArchitectureConfig", "ConfigError", "config_from_json", "known_architectures",
            "load_model_config", "register_architecture", "LayerSpec", "ModelSpec", "PagedCacheNeed", "PartSpec",
-           "RunEntry", "StateCacheNeed", "CompositeCacheNeed", "Qwen3Config", "NezolornConfig"]
+           "RunEntry", "StateCacheNeed", "CompositeCacheNeed", "Qwen3Config", "NezolornConfig", "DaronexConfig"]

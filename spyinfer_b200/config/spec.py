@@ -107,7 +107,9 @@ class PagedCacheNeed:
     positions (the query's own included) whose entries the mixer still reads; older pages are
     given back.  ``stride`` above 1: the mixer keeps one entry for every ``stride`` tokens (a
     summary of each block of that many tokens, stored when the block's last token is), so a
-    request of ``L`` tokens holds ``L // stride`` entries; such a need has no window.  Entries of
+    request of ``L`` tokens holds ``L // stride`` entries; such a need has no window.  ``planes``
+    is 2 for keys and values, 1 for a mixer whose values are its keys (or a part of them, as a
+    latent that keys and values are both projected from): a page then holds keys only.  Entries of
     the run order with equal needs share one group of pages in the cache manager.
     """
 
@@ -115,13 +117,16 @@ class PagedCacheNeed:
     head_dim: int
     window: Optional[int] = None
     stride: int = 1
+    planes: int = 2
 
     def __post_init__(self):
+        if self.planes not in (1, 2):
+            raise ValueError(f"a paged need has 1 or 2 planes, found {self.planes}")
         if self.stride < 1 or (self.stride > 1 and self.window is not None):
             raise ValueError(f"a paged need's stride must be at least 1, and with a stride above 1 there is no window (found stride {self.stride}, window {self.window})")
 
     def group_key(self) -> Tuple:
-        return ("paged", self.num_kv_heads, self.head_dim, self.window, self.stride)
+        return ("paged", self.num_kv_heads, self.head_dim, self.window, self.stride, self.planes)
 
 
 @dataclass(frozen=True)

@@ -85,6 +85,7 @@ struct Params {
     float* part_ml;            // [slots][G][2]  (maximum in the log2 domain, sum)
     int* status;
     int table_width, page_size, num_pages, nh, nkv, G, S, window, blocks, max_keys, mode;
+    int planes;                // 2: a page holds keys and values; 1: keys only, and the values are the keys
     int hd;                    // the head size as stored (a multiple of 8, at most HD): the tiles are HD wide, what lies beyond hd is zero
     float scale_log2;
 };
@@ -583,7 +584,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (!ok) break;
                 if (lane < boxes) {
-                    const int y = ((page * 2 + kv) * p.nkv + g.kvh) * p.page_size;
+                    const int y = ((page * p.planes + kv * (p.planes - 1)) * p.nkv + g.kvh) * p.page_size;
                     tma_load_2d(ring + stage * STAGE_BYTES + my_half * HALF_BYTES + my_page * p.page_size * 128, &page_map, my_half * 64, y, bar_full + stage);
                 }
             }
@@ -636,9 +637,10 @@ extern "C" long long spy_attention_decode_scratch_floats(int seqs, int nh, int n
 static int run_attention_decode(const void* q, long long q_row_stride, void* out, float* lse, const void* pages, const int* block_table, int table_width,
                                 int page_size, int num_pages, int nh, int nkv, int hd, const int* positions, const int* q_start, int tokens,
                                 int seqs, int window, float scale, int mode, float* scratch, long long scratch_floats, int* status,
-                                cudaStream_t stream)
+                                cudaStream_t stream, int planes)
 {
     if (tokens <= 0 || seqs <= 0) return 0;
+    if (planes != 1 && planes != 2) SPY_FAIL("attention_decode: a cache of %d planes (1 or 2)", planes);
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) SPY_FAIL("attention_decode: %d query heads do not group over %d key/value heads", nh, nkv);
     const int G = nh / nkv;
     if (G > NCOLS) SPY_FAIL("attention_decode: %d query heads per key/value head exceed %d", G, NCOLS);
@@ -664,15 +666,16 @@ static int run_attention_decode(const void* q, long long q_row_stride, void* out
     if (encode == nullptr) SPY_FAIL("attention_decode: cuTensorMapEncodeTiled is not available from the driver");
 
     Params p;
+    p.planes = planes;
     p.out = (bf16*)out; p.lse = lse; p.block_table = block_table; p.positions = positions; p.q_start = q_start; p.status = status;
     p.part_o = scratch; p.part_ml = scratch + ((size_t)seqs * nkv + sms) * G * hd_tile;
     p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages; p.nh = nh; p.nkv = nkv; p.G = G; p.S = seqs;
     p.window = window; p.hd = hd; p.blocks = sms; p.max_keys = (int)max_keys; p.mode = mode; p.scale_log2 = scale * LOG2E;
 
-    // the pages of this cache as one matrix [num_pages * 2 * nkv * page_size rows, hd]; a box is one page's rows x 64 columns
+    // the pages of this cache as one matrix [num_pages * planes * nkv * page_size rows, hd] (planes = 1: keys only, and the values are the keys); a box is one page's rows x 64 columns
     CUtensorMap page_map, q_map;
     {
-        cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)num_pages * 2 * nkv * page_size};
+        cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)num_pages * planes * nkv * page_size};
         cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
         cuuint32_t box[2] = {64, (cuuint32_t)page_size};
         cuuint32_t elem[2] = {1, 1};
@@ -699,10 +702,10 @@ static int run_attention_decode(const void* q, long long q_row_stride, void* out
 extern "C" int spy_attention_decode(const void* q, long long q_row_stride, void* out, const void* pages, const int* block_table, int table_width,
                                     int page_size, int num_pages, int nh, int nkv, int hd, const int* positions, const int* q_start, int tokens,
                                     int seqs, int window, float scale, int mode, float* scratch, long long scratch_floats, int* status,
-                                    cudaStream_t stream)
+                                    cudaStream_t stream, int planes)
 {
     return run_attention_decode(q, q_row_stride, out, nullptr, pages, block_table, table_width, page_size, num_pages, nh, nkv, hd, positions, q_start, tokens,
-                                seqs, window, scale, mode, scratch, scratch_floats, status, stream);
+                                seqs, window, scale, mode, scratch, scratch_floats, status, stream, planes);
 }
 
 // The same, and lse [tokens, nh] (float32) receives, for every sequence's token and head, the natural logarithm of its sum of
@@ -710,9 +713,9 @@ extern "C" int spy_attention_decode(const void* q, long long q_row_stride, void*
 extern "C" int spy_attention_decode_lse(const void* q, long long q_row_stride, void* out, float* lse, const void* pages, const int* block_table,
                                         int table_width, int page_size, int num_pages, int nh, int nkv, int hd, const int* positions, const int* q_start,
                                         int tokens, int seqs, int window, float scale, int mode, float* scratch, long long scratch_floats, int* status,
-                                        cudaStream_t stream)
+                                        cudaStream_t stream, int planes)
 {
     if (lse == nullptr) SPY_FAIL("attention_decode: no place for the logarithms of the sums");
     return run_attention_decode(q, q_row_stride, out, lse, pages, block_table, table_width, page_size, num_pages, nh, nkv, hd, positions, q_start, tokens,
-                                seqs, window, scale, mode, scratch, scratch_floats, status, stream);
+                                seqs, window, scale, mode, scratch, scratch_floats, status, stream, planes);
 }

@@ -2,7 +2,9 @@
 // This is the plain kernel: it takes every head size (a multiple of 4 elements), every page
 // size, 32-bit or bfloat16 storage, and computes everything in 32-bit with expf.  It is the
 // engine's float32 path and the fallback of the bfloat16 path for sizes its fast kernels
-// refuse.
+// refuse.  A cache of one plane (`planes` = 1) holds keys only and the values are the keys
+// themselves (a latent that both are made of): V rows are then read from the K plane.  Head
+// sizes that are no multiple of 4 take element-wise loads.
 //
 // A query at position p of sequence s sees the keys j with lo <= j <= p, lo = 0 or
 // p - window + 1; key j lies in page block_table[s, j / page_size], slot j % page_size.
@@ -38,13 +40,13 @@ template <typename TA, typename TC>
 __global__ void __launch_bounds__(CHUNK)
 attention_generic_kernel(const TA* __restrict__ q, long long q_row_stride, TA* __restrict__ out, const TC* __restrict__ pages,
                          const int* __restrict__ block_table, int table_width, int page_size, int num_pages, int nh, int nkv, int hd,
-                         const int* __restrict__ positions, const int* __restrict__ seq_of_token, int window, float scale, int* status)
+                         const int* __restrict__ positions, const int* __restrict__ seq_of_token, int window, float scale, int* status, int planes)
 {
     extern __shared__ float smem[];
     pdl_enter();
     float* q_s = smem;                       // hd
     float* p_s = q_s + hd;                   // CHUNK
-    long long* row_s = (long long*)(p_s + CHUNK);  // CHUNK offsets of K rows (elements); 8-byte aligned: hd % 4 == 0, CHUNK even
+    long long* row_s = (long long*)(p_s + CHUNK + (hd & 1));  // CHUNK offsets of K rows (elements); 8-byte aligned: hd + (hd & 1) and CHUNK are even
     float* scratch = (float*)(row_s + CHUNK);      // 33
 
     const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
@@ -52,7 +54,8 @@ attention_generic_kernel(const TA* __restrict__ q, long long q_row_stride, TA* _
     const int seq = seq_of_token[t];
     const int kvh = h / (nh / nkv);
     const int* bt = block_table + (size_t)seq * table_width;
-    const long long v_offset = (long long)nkv * page_size * hd;  // from a K row to its V row
+    const long long v_offset = planes == 2 ? (long long)nkv * page_size * hd : 0;  // from a K row to its V row (one plane: the values are the keys)
+    const bool quads = (hd & 3) == 0;
 
     const TA* q_row = q + (size_t)t * q_row_stride + (size_t)h * hd;
     for (int d = tid; d < hd; d += CHUNK) q_s[d] = to_f32(q_row[d]);
@@ -73,20 +76,24 @@ attention_generic_kernel(const TA* __restrict__ q, long long q_row_stride, TA* _
                 report_status(status, SPY_STATUS_BAD_PAGE, t);
                 valid = false;
             } else {
-                row = ((((long long)page * 2) * nkv + kvh) * page_size + j % page_size) * hd;
+                row = ((((long long)page * planes) * nkv + kvh) * page_size + j % page_size) * hd;
             }
         }
         float s = -INFINITY;
         if (valid) {
             const TC* k = pages + row;
             float dot = 0.f;
-            for (int d = 0; d < hd; d += 4) {
-                float kv[4];
-                Vec4<TC>::load(k + d, kv);
-                dot = fmaf(q_s[d], kv[0], dot);
-                dot = fmaf(q_s[d + 1], kv[1], dot);
-                dot = fmaf(q_s[d + 2], kv[2], dot);
-                dot = fmaf(q_s[d + 3], kv[3], dot);
+            if (quads) {
+                for (int d = 0; d < hd; d += 4) {
+                    float kv[4];
+                    Vec4<TC>::load(k + d, kv);
+                    dot = fmaf(q_s[d], kv[0], dot);
+                    dot = fmaf(q_s[d + 1], kv[1], dot);
+                    dot = fmaf(q_s[d + 2], kv[2], dot);
+                    dot = fmaf(q_s[d + 3], kv[3], dot);
+                }
+            } else {
+                for (int d = 0; d < hd; ++d) dot = fmaf(q_s[d], to_f32(k[d]), dot);
             }
             s = dot * scale;
         }
@@ -121,25 +128,26 @@ attention_generic_kernel(const TA* __restrict__ q, long long q_row_stride, TA* _
 }
 
 // q: [T, ...] rows of q_row_stride elements whose first nh*hd elements are the query heads;
-// out: [T, nh*hd]; pages: one cache [num_pages][2][nkv][page_size][hd] of cache_dtype.
+// out: [T, nh*hd]; pages: one cache [num_pages][planes][nkv][page_size][hd] of cache_dtype.
 extern "C" int spy_attention_generic(const void* q, long long q_row_stride, void* out, int act_dtype, const void* pages, int cache_dtype,
                                      const int* block_table, int table_width, int page_size, int num_pages, int nh, int nkv, int hd,
                                      const int* positions, const int* seq_of_token, int tokens, int window, float scale, int* status,
-                                     cudaStream_t stream)
+                                     cudaStream_t stream, int planes)
 {
     if (tokens <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) SPY_FAIL("attention: %d query heads do not group over %d key/value heads", nh, nkv);
-    if (hd <= 0 || hd % 4 != 0 || hd > 4 * CHUNK) SPY_FAIL("attention: head_dim %d must be a multiple of 4, at most %d", hd, 4 * CHUNK);
+    if (hd <= 0 || hd > 4 * CHUNK) SPY_FAIL("attention: head_dim %d must be positive and at most %d", hd, 4 * CHUNK);
+    if (planes != 1 && planes != 2) SPY_FAIL("attention: a cache of %d planes (1: keys that are the values too, 2: keys and values)", planes);
     if (page_size <= 0 || num_pages <= 0 || table_width <= 0) SPY_FAIL("attention: page_size, num_pages and table_width must be positive");
     if (window < 0) SPY_FAIL("attention: window %d must be 0 (none) or positive", window);
     if (nh > 65535) SPY_FAIL("attention: %d heads exceed the grid limit", nh);
-    const size_t smem = (size_t)(hd + CHUNK + 33) * sizeof(float) + (size_t)CHUNK * sizeof(long long);
+    const size_t smem = (size_t)(hd + (hd & 1) + CHUNK + 33) * sizeof(float) + (size_t)CHUNK * sizeof(long long);
     dim3 grid(tokens, nh);
     SPY_DISPATCH_DTYPE(act_dtype, TA, {
         SPY_DISPATCH_DTYPE(cache_dtype, TC, {
             spy_launch(attention_generic_kernel<TA, TC>, grid, dim3(CHUNK), smem, stream,
                 (const TA*)q, q_row_stride, (TA*)out, (const TC*)pages, block_table, table_width, page_size, num_pages, nh, nkv, hd,
-                positions, seq_of_token, window, scale, status);
+                positions, seq_of_token, window, scale, status, planes);
         })
     })
     SPY_CHECK_LAUNCH("attention_generic");

@@ -75,6 +75,7 @@ struct Params {
     const int* q_start;        // [S + 1]
     int* status;
     int table_width, page_size, num_pages, nh, nkv, G, Gp, S, window;
+    int planes;                // 2: a page holds keys and values; 1: keys only, and the values are the keys
     int hd;                    // the head size as stored (a multiple of 8, at most HD): the tiles are HD wide, what lies beyond hd is zero
     int x_blocks, items;       // 256-row blocks along the tokens (an upper bound), and x_blocks * nkv work items
     float scale_log2;
@@ -509,7 +510,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (!ok) break;
                 if (valid) {
-                    const int y = ((page * 2 + kv) * p.nkv + it.kvh) * p.page_size;
+                    const int y = ((page * p.planes + kv * (p.planes - 1)) * p.nkv + it.kvh) * p.page_size;
                     tma_load_2d((kv == 0 ? k_s : v_s) + st * L::OPERAND_BYTES + my_half * (ROWS * 128) + my_page * p.page_size * 128, &page_map, my_half * 64, y, bar);
                 }
             }
@@ -539,9 +540,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
 // Attention of a batch over its pages: prompt portions, any mix, single tokens included.
 static int run_attention_tc(const void* q, long long q_row_stride, void* out, float* lse, const void* pages, const int* block_table, int table_width,
                             int page_size, int num_pages, int nh, int nkv, int hd, const int* positions, const int* q_start, int tokens,
-                            int seqs, int window, float scale, int* status, cudaStream_t stream)
+                            int seqs, int window, float scale, int* status, cudaStream_t stream, int planes)
 {
     if (tokens <= 0 || seqs <= 0) return 0;
+    if (planes != 1 && planes != 2) SPY_FAIL("attention_tc: a cache of %d planes (1 or 2)", planes);
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) SPY_FAIL("attention_tc: %d query heads do not group over %d key/value heads", nh, nkv);
     const int G = nh / nkv;
     if (G > 16) SPY_FAIL("attention_tc: %d query heads per key/value head exceed 16", G);
@@ -553,18 +555,19 @@ static int run_attention_tc(const void* q, long long q_row_stride, void* out, fl
     if (window < 0) SPY_FAIL("attention_tc: window %d must be 0 (none) or positive", window);
     const int Gp = G;   // rows a token takes in a query tile: one per head of the group (128 / G tokens a tile, the remainder of the rows stays empty)
     Params p;
+    p.planes = planes;
     p.q = (const bf16*)q; p.q_stride = q_row_stride; p.out = (bf16*)out; p.lse = lse; p.block_table = block_table;
     p.positions = positions; p.q_start = q_start; p.status = status; p.table_width = table_width; p.page_size = page_size;
     p.num_pages = num_pages; p.nh = nh; p.nkv = nkv; p.G = G; p.Gp = Gp; p.S = seqs; p.window = window; p.hd = hd; p.scale_log2 = scale * LOG2E;
     if (page_size < 8 || page_size > TILE || TILE % page_size != 0)
         SPY_FAIL("attention_tc: page_size %d must be 8, 16, 32, 64 or 128 (one TMA box per page)", page_size);
-    // the pages of this cache as one matrix [num_pages * 2 * nkv * page_size rows, hd]; a box is one page's rows x 64 columns
+    // the pages of this cache as one matrix [num_pages * planes * nkv * page_size rows, hd] (planes = 1: keys only, and the values are the keys); a box is one page's rows x 64 columns
     // (columns beyond hd are outside the matrix and arrive as zeros: a head size below the tile's 64 or 128 is padded on the way in)
     tc::EncodeTiledFn encode = tc::encode_tiled_fn();
     if (encode == nullptr) SPY_FAIL("attention_tc: cuTensorMapEncodeTiled is not available from the driver");
     CUtensorMap page_map;
     {
-        cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)num_pages * 2 * nkv * page_size};
+        cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)num_pages * planes * nkv * page_size};
         cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
         cuuint32_t box[2] = {64, (cuuint32_t)page_size};
         cuuint32_t elem[2] = {1, 1};
@@ -595,19 +598,19 @@ static int run_attention_tc(const void* q, long long q_row_stride, void* out, fl
 
 extern "C" int spy_attention_tc(const void* q, long long q_row_stride, void* out, const void* pages, const int* block_table, int table_width,
                                 int page_size, int num_pages, int nh, int nkv, int hd, const int* positions, const int* q_start, int tokens,
-                                int seqs, int window, float scale, int* status, cudaStream_t stream)
+                                int seqs, int window, float scale, int* status, cudaStream_t stream, int planes)
 {
     return run_attention_tc(q, q_row_stride, out, nullptr, pages, block_table, table_width, page_size, num_pages, nh, nkv, hd, positions, q_start, tokens, seqs,
-                            window, scale, status, stream);
+                            window, scale, status, stream, planes);
 }
 
 // The same, and lse [tokens, nh] (float32) receives the natural logarithm of every (token, head)'s sum of exp(score * scale):
 // with it a caller can merge further keys into the softmax afterwards.
 extern "C" int spy_attention_tc_lse(const void* q, long long q_row_stride, void* out, float* lse, const void* pages, const int* block_table,
                                     int table_width, int page_size, int num_pages, int nh, int nkv, int hd, const int* positions, const int* q_start,
-                                    int tokens, int seqs, int window, float scale, int* status, cudaStream_t stream)
+                                    int tokens, int seqs, int window, float scale, int* status, cudaStream_t stream, int planes)
 {
     if (lse == nullptr) SPY_FAIL("attention_tc: no place for the logarithms of the sums");
     return run_attention_tc(q, q_row_stride, out, lse, pages, block_table, table_width, page_size, num_pages, nh, nkv, hd, positions, q_start, tokens, seqs,
-                            window, scale, status, stream);
+                            window, scale, status, stream, planes);
 }

@@ -4,7 +4,9 @@
 //                                            a = exp(f + m - m'), b = exp(i - m');
 //   * the generalised delta rule:            S = diag(w) S - (r u)(u^T S) + k v^T,  o = S^T q,  u = k / sqrt(sum k^2 + 1e-6),
 //                                            both terms reading the old S, w a decay and r a removal rate per key channel;
-// and what follows both: each head's output divided by its root mean square, times a weight, times a sigmoid gate.
+//   * gated linear attention:                S = diag(a) S + k v^T,  o = S^T q,  a = sigmoid(z)^(1/tau) = exp(logsigmoid(z) / tau)
+//                                            a decay per key channel from the pre-activation z;
+// and what follows them: each head's output divided by its root mean square, times a weight, times a gate (sigmoid or SiLU).
 //
 // A block owns a tile of value columns of one (request, head) (32, 16 or 8 of them: whatever gives the SMs a block each) and
 // walks the request's tokens of this step in order, with its part of S in registers.  The columns of S do not depend on one
@@ -38,9 +40,9 @@ struct ScanArgs {
     const float* proj;      // [T, ld]
     long long ld;
     int off_q, off_k, off_v, off_x1, off_x2;   // columns of q (or r), k, v; mLSTM: i and f pre-activations; delta: the removal rate's pre-activation (x2 unused)
-    const float* extra;     // delta: the decay's pre-activation [T, H * dk]
+    const float* extra;     // delta, gated linear attention: the decay's pre-activation [T, H * dk]
     const float* bias1;     // mLSTM: bias of i [H];   delta: bias of the removal rate [H * dk]
-    const float* bias2;     // mLSTM: bias of f [H];   delta: the decay's offset [H * dk]
+    const float* bias2;     // mLSTM: bias of f [H];   delta: the decay's offset [H * dk];   gated linear attention: the decay's bias [H * dk]
     float* state;           // [slots, H, record]
     long long record;       // floats a head: mLSTM dk * dv + (dk + 1) for every 8 columns (padded to 4); delta dk * dv
     int num_slots;
@@ -48,7 +50,7 @@ struct ScanArgs {
     const int* state_slot;  // [S]
     float* out;             // [T, H * dv]
     int H, dk, dv;
-    float q_scale, cap;
+    float q_scale, cap;     // cap: mLSTM: the gates' cap;   gated linear attention: 1 / tau
     int* status;
 };
 
@@ -66,7 +68,7 @@ constexpr int THREADS = 256;      // 8 warps; warp w owns the columns 4w .. 4w +
 // token run beside those of the others and beside the next token's rows (nothing in S waits for them).
 // RG row groups share a warp's lanes (8, 16 or 32), so a warp owns 32 / RG columns and a block CTB = 8 * 32 / RG of them:
 // with few requests and heads the tiles are made narrow, so that there are blocks for every SM, and a thread's rows few.
-template <int MODE, int NR, int RG>   // MODE 0: gated matrix memory, 1: delta rule
+template <int MODE, int NR, int RG>   // MODE 0: gated matrix memory, 1: delta rule, 2: gated linear attention
 __global__ void __launch_bounds__(THREADS, NR <= 8 ? 2 : 1) scan_kernel(ScanArgs A, int TC)
 {
     constexpr int CW = 32 / RG, CTB = 8 * CW, SPB = CTB + 4;   // columns a warp and a block own; floats between the rows of the state tile in shared memory
@@ -78,7 +80,8 @@ __global__ void __launch_bounds__(THREADS, NR <= 8 ? 2 : 1) scan_kernel(ScanArgs
     constexpr int V4 = NR >= 4 ? 4 : NR;           // elements a load of a thread's rows brings
     const int dk = A.dk, dv = A.dv, H = A.H;
     // two stages of a chunk's vectors (the next chunk's arrive while this one's tokens are walked), then what a chunk makes
-    const size_t stage_floats = (size_t)(MODE == 1 ? 4 : 2) * TC * KS + (size_t)TC * CTB + 2 * (size_t)TC;
+    constexpr int NVEC = MODE == 1 ? 4 : (MODE == 2 ? 3 : 2);     // staged vectors of dk a token: k, q, then the removal rate (delta) and the decay (delta, gated linear attention)
+    const size_t stage_floats = (size_t)NVEC * TC * KS + (size_t)TC * CTB + 2 * (size_t)TC;
     float* o_s = sm + 2 * stage_floats;            // [TC][CTB]
     float* m_s = o_s + TC * CTB;                   // [TC] memory: the running maximum after each token
     float* nqp = m_s + TC;                         // [TC][8] memory: n . q, one partial sum a warp
@@ -119,7 +122,7 @@ __global__ void __launch_bounds__(THREADS, NR <= 8 ? 2 : 1) scan_kernel(ScanArgs
 
     // whether a token's vectors start on 16-byte boundaries in the projection (and in the decay's pre-activation)
     const bool aligned = (dk & 3) == 0 && (A.ld & 3) == 0 && ((A.off_k | A.off_q) & 3) == 0 && (reinterpret_cast<uintptr_t>(A.proj) & 15) == 0 &&
-                         (MODE == 0 || ((A.off_x1 & 3) == 0 && (reinterpret_cast<uintptr_t>(A.extra) & 15) == 0));
+                         (MODE == 0 || (((MODE == 1 ? A.off_x1 : 0) & 3) == 0 && (reinterpret_cast<uintptr_t>(A.extra) & 15) == 0));
     // Requests a chunk's vectors into a stage: 16-byte asynchronous copies where the columns allow it (all under way at once),
     // else plain loads; v and the gates' pre-activations by 4-byte copies.  What is made of them (the scaled q, the sigmoid of
     // the removal rate, the decay, the capped gates) is worked out in place once they have landed.
@@ -129,7 +132,7 @@ __global__ void __launch_bounds__(THREADS, NR <= 8 ? 2 : 1) scan_kernel(ScanArgs
         float* q_s = k_s + (size_t)TC * KS;
         float* x1_s = q_s + (size_t)TC * KS;
         float* x2_s = x1_s + (MODE == 1 ? (size_t)TC * KS : 0);
-        float* v_s = x2_s + (MODE == 1 ? (size_t)TC * KS : 0);
+        float* v_s = x2_s + (MODE != 0 ? (size_t)TC * KS : 0);
         float* g1_s = v_s + TC * CTB;
         float* g2_s = g1_s + TC;
         if (aligned) {
@@ -139,10 +142,8 @@ __global__ void __launch_bounds__(THREADS, NR <= 8 ? 2 : 1) scan_kernel(ScanArgs
                 const float* row = A.proj + (size_t)(t0 + tt) * A.ld;
                 cp_async16(k_s + tt * KS + 4 * qd, row + A.off_k + c);
                 cp_async16(q_s + tt * KS + 4 * qd, row + A.off_q + c);
-                if (MODE == 1) {
-                    cp_async16(x1_s + tt * KS + 4 * qd, row + A.off_x1 + c);
-                    cp_async16(x2_s + tt * KS + 4 * qd, A.extra + (size_t)(t0 + tt) * H * dk + c);
-                }
+                if (MODE == 1) cp_async16(x1_s + tt * KS + 4 * qd, row + A.off_x1 + c);
+                if (MODE != 0) cp_async16(x2_s + tt * KS + 4 * qd, A.extra + (size_t)(t0 + tt) * H * dk + c);
             }
         } else {
             for (int idx = tid; idx < n_tok * dk; idx += THREADS) {
@@ -150,10 +151,8 @@ __global__ void __launch_bounds__(THREADS, NR <= 8 ? 2 : 1) scan_kernel(ScanArgs
                 const float* row = A.proj + (size_t)(t0 + tt) * A.ld;
                 cp_async4(k_s + tt * KS + r, row + A.off_k + c);
                 cp_async4(q_s + tt * KS + r, row + A.off_q + c);
-                if (MODE == 1) {
-                    cp_async4(x1_s + tt * KS + r, row + A.off_x1 + c);
-                    cp_async4(x2_s + tt * KS + r, A.extra + (size_t)(t0 + tt) * H * dk + c);
-                }
+                if (MODE == 1) cp_async4(x1_s + tt * KS + r, row + A.off_x1 + c);
+                if (MODE != 0) cp_async4(x2_s + tt * KS + r, A.extra + (size_t)(t0 + tt) * H * dk + c);
             }
         }
         if (KS > dk) {
@@ -162,7 +161,8 @@ __global__ void __launch_bounds__(THREADS, NR <= 8 ? 2 : 1) scan_kernel(ScanArgs
                 const int tt = idx / pad, r = dk + idx - tt * pad;
                 k_s[tt * KS + r] = 0.f;
                 q_s[tt * KS + r] = 0.f;
-                if (MODE == 1) { x1_s[tt * KS + r] = 0.f; x2_s[tt * KS + r] = 0.f; }
+                if (MODE == 1) x1_s[tt * KS + r] = 0.f;
+                if (MODE != 0) x2_s[tt * KS + r] = 0.f;
             }
         }
         for (int idx = tid; idx < n_tok * CTB; idx += THREADS) {
@@ -185,7 +185,7 @@ __global__ void __launch_bounds__(THREADS, NR <= 8 ? 2 : 1) scan_kernel(ScanArgs
         float* q_s = k_s + (size_t)TC * KS;
         float* x1_s = q_s + (size_t)TC * KS;
         float* x2_s = x1_s + (MODE == 1 ? (size_t)TC * KS : 0);
-        float* v_s = x2_s + (MODE == 1 ? (size_t)TC * KS : 0);
+        float* v_s = x2_s + (MODE != 0 ? (size_t)TC * KS : 0);
         float* g1_s = v_s + TC * CTB;
         float* g2_s = g1_s + TC;
         cp_async_wait_all();
@@ -194,6 +194,9 @@ __global__ void __launch_bounds__(THREADS, NR <= 8 ? 2 : 1) scan_kernel(ScanArgs
             const int tt = idx / dk, r = idx - tt * dk, c = h * dk + r;
             if (MODE == 0) {
                 q_s[tt * KS + r] *= A.q_scale;
+            } else if (MODE == 2) {
+                q_s[tt * KS + r] *= A.q_scale;
+                x2_s[tt * KS + r] = expf(log_sigmoidf_(x2_s[tt * KS + r] + A.bias2[c]) * A.cap);
             } else {
                 x1_s[tt * KS + r] = sigmoidf_(x1_s[tt * KS + r] + A.bias1[c]);
                 x2_s[tt * KS + r] = expf(-0.60653065971263342f * sigmoidf_(x2_s[tt * KS + r] + A.bias2[c]));   // exp(-1/2) = 0.6065...
@@ -280,6 +283,28 @@ __global__ void __launch_bounds__(THREADS, NR <= 8 ? 2 : 1) scan_kernel(ScanArgs
                             nq[u] += n_reg[j] * q_s[tt * KS + r];
                         }
                     }
+                } else if (MODE == 2) {
+                    const float* __restrict__ decay = x2_s + tt * KS + r0;
+                    float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int i0 = 0; i0 < NR; i0 += V4) {
+                        float kk[V4], qq[V4], dd[V4];
+                        if (V4 == 4) {
+                            *reinterpret_cast<float4*>(kk) = *reinterpret_cast<const float4*>(k + i0);
+                            *reinterpret_cast<float4*>(qq) = *reinterpret_cast<const float4*>(q + i0);
+                            *reinterpret_cast<float4*>(dd) = *reinterpret_cast<const float4*>(decay + i0);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < V4; ++e) { kk[e] = k[i0 + e]; qq[e] = q[i0 + e]; dd[e] = decay[i0 + e]; }
+                        }
+#pragma unroll
+                        for (int e = 0; e < V4; ++e) {
+                            const float s = fmaf(dd[e], Sr[i0 + e], kk[e] * v_c);
+                            Sr[i0 + e] = s;
+                            part[e & 3] = fmaf(s, qq[e], part[e & 3]);
+                        }
+                    }
+                    acc[u] = (part[0] + part[1]) + (part[2] + part[3]);
                 } else {
                     const float inv = g1_s[tt];
                     const float* __restrict__ rate = x1_s + tt * KS + r0;
@@ -394,7 +419,7 @@ __global__ void __launch_bounds__(THREADS, NR <= 16 ? 4 : 1) scan_decode_kernel(
 #pragma unroll
     for (int i = 0; i < NR; ++i) Sr[i] = (r0 + i < dk && col_ok) ? st[(size_t)(r0 + i) * dv + c0 + lane] : 0.f;
     const float* row = A.proj + (size_t)t * A.ld;
-    float *k_s = vec, *q_s = vec + dk, *x1_s = vec + 2 * dk, *x2_s = vec + 3 * dk;
+    float *k_s = vec, *q_s = vec + dk, *x1_s = vec + 2 * dk, *x2_s = vec + (MODE == 1 ? 3 : 2) * dk;     // gated linear attention has no x1
     float a = 1.f, b = 0.f, m_new = 0.f, ksq = 0.f, nq = 0.f;
     float* st_nm = st + (size_t)dk * dv + (size_t)(c0 / 8) * (dk + 1);      // n and m: a copy for every 8 columns; the first of this tile's is read, all of them are written
     const int copies = min(CT / 8, (dv + 7) / 8 - c0 / 8);
@@ -415,6 +440,8 @@ __global__ void __launch_bounds__(THREADS, NR <= 16 ? 4 : 1) scan_decode_kernel(
             const float n = a * st_nm[r] + b * kr;
             for (int cp = 0; cp < copies; ++cp) st_nm[(size_t)cp * (dk + 1) + r] = n;
             nq += n * qr;
+        } else if (MODE == 2) {
+            x2_s[r] = expf(log_sigmoidf_(A.extra[(size_t)t * H * dk + c] + A.bias2[c]) * A.cap);
         } else {
             x1_s[r] = sigmoidf_(row[A.off_x1 + c] + A.bias1[c]);
             x2_s[r] = expf(-0.60653065971263342f * sigmoidf_(A.extra[(size_t)t * H * dk + c] + A.bias2[c]));
@@ -424,7 +451,7 @@ __global__ void __launch_bounds__(THREADS, NR <= 16 ? 4 : 1) scan_decode_kernel(
     if (MODE == 0) {
         nq = warp_sum(nq);
         if (lane == 0) nqp[warp] = nq;
-    } else {
+    } else if (MODE == 1) {
         ksq = warp_sum(ksq);
         if (lane == 0) part[warp] = ksq;
     }
@@ -451,6 +478,24 @@ __global__ void __launch_bounds__(THREADS, NR <= 16 ? 4 : 1) scan_decode_kernel(
         }
         if (tid == 0)
             for (int cp = 0; cp < copies; ++cp) st_nm[(size_t)cp * (dk + 1) + dk] = m_new;
+    } else if (MODE == 2) {
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+            const int r = r0 + i;
+            if (r < dk) {
+                const float s = fmaf(x2_s[r], Sr[i], k_s[r] * v_c);
+                if (col_ok) st[(size_t)r * dv + c0 + lane] = s;
+                acc = fmaf(s, q_s[r], acc);
+            }
+        }
+        red2[warp][lane] = acc;
+        __syncthreads();
+        if (warp == 0 && col_ok) {
+            float o = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) o += red2[w][lane];
+            A.out[(size_t)t * H * dv + h * dv + c0 + lane] = o;
+        }
     } else {
         float sq = 0.f;
 #pragma unroll
@@ -497,7 +542,7 @@ template <int MODE, int RG> static int launch_scan_rg(ScanArgs& A, int num_seqs,
     int tc = 32;
     while (tc > 1 && tc / 2 >= longest) tc /= 2;
     auto bytes = [&](int n) {
-        const size_t stage = (MODE == 1 ? 4 : 2) * (size_t)n * RG * nr + (size_t)n * CTB + 2 * (size_t)n;      // one stage of a chunk's vectors
+        const size_t stage = (MODE == 1 ? 4 : (MODE == 2 ? 3 : 2)) * (size_t)n * RG * nr + (size_t)n * CTB + 2 * (size_t)n;      // one stage of a chunk's vectors
         const size_t staged = (2 * stage + (size_t)n * CTB + 11 * (size_t)n) * sizeof(float);
         const size_t tile = (size_t)A.dk * (CTB + 4) * sizeof(float);
         return staged > tile ? staged : tile;
@@ -536,7 +581,7 @@ template <int MODE> static int launch_scan_mode(ScanArgs& A, int num_seqs, int l
             case 32: dk_kernel = scan_decode_kernel<MODE, 32>; break;
             default: dk_kernel = scan_decode_kernel<MODE, 64>; break;
         }
-        const size_t vec_bytes = (MODE == 1 ? 4 : 2) * (size_t)A.dk * sizeof(float);
+        const size_t vec_bytes = (MODE == 1 ? 4 : (MODE == 2 ? 3 : 2)) * (size_t)A.dk * sizeof(float);
         spy_launch(dk_kernel, dim3(num_seqs, A.H, tiles), dim3(THREADS), vec_bytes, stream, A);
         SPY_CHECK_LAUNCH("recurrence scan (decoding)");
         return 0;
@@ -564,6 +609,7 @@ static int launch_scan(int mode, ScanArgs& A, int num_seqs, int longest, cudaStr
     if (A.H <= 0 || A.dk <= 0 || A.dv <= 0) SPY_FAIL("recurrence: heads %d, key size %d and value size %d must be positive", A.H, A.dk, A.dv);
     if (A.H > 65535) SPY_FAIL("recurrence: %d heads exceed the grid limit", A.H);
     if ((A.dv + CT - 1) / CT > 65535) SPY_FAIL("recurrence: a value size of %d exceeds the grid limit", A.dv);
+    if (mode == 2) return launch_scan_mode<2>(A, num_seqs, longest, stream);
     return mode == 0 ? launch_scan_mode<0>(A, num_seqs, longest, stream) : launch_scan_mode<1>(A, num_seqs, longest, stream);
 }
 
@@ -589,11 +635,23 @@ extern "C" int spy_delta_scan(const float* proj, long long ld, int off_r, int of
     return launch_scan(1, A, num_seqs, longest, stream);
 }
 
-// ---- what follows a recurrence: unit root mean square per head, a weight, a sigmoid gate -------------
+// Gated linear attention with a decay per key channel: proj holds q, k, v at `off_*`; decay_pre [T, H * dk] the decay's
+// pre-activation z, to which decay_bias [H * dk] is added: a = exp(logsigmoid(z + bias) / tau).  q is scaled by q_scale.
+extern "C" int spy_gla_scan(const float* proj, long long ld, int off_q, int off_k, int off_v, const float* decay_pre, const float* decay_bias, float inv_tau,
+                            float* state, int num_slots, const int* q_start, const int* state_slot, int num_seqs, int longest, float* out, int H, int dk, int dv,
+                            float q_scale, int* status, cudaStream_t stream)
+{
+    if (!(inv_tau > 0.f)) SPY_FAIL("gated linear attention: tau must be positive");
+    ScanArgs A = {proj, ld, off_q, off_k, off_v, 0, 0, decay_pre, nullptr, decay_bias, state, (long long)dk * dv, num_slots, q_start, state_slot, out,
+                  H, dk, dv, q_scale, inv_tau, status};
+    return launch_scan(2, A, num_seqs, longest, stream);
+}
+
+// ---- what follows a recurrence: unit root mean square per head, a weight, a gate (sigmoid, or SiLU) -------------
 // One warp a (token, head) row, eight rows a block: the row's sum of squares is a sum inside the warp.
 template <typename TO>
 __global__ void gated_head_norm_kernel(const float* __restrict__ o, const float* __restrict__ proj, long long ld, int off_g, const float* __restrict__ weight,
-                                       TO* __restrict__ out, long long rows, int H, int dv, float eps)
+                                       TO* __restrict__ out, long long rows, int H, int dv, float eps, int gate_act)
 {
     pdl_enter();
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -607,45 +665,51 @@ __global__ void gated_head_norm_kernel(const float* __restrict__ o, const float*
     ss = warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
     const float* g = proj + t * ld + off_g + h * dv;
-    for (int c = lane; c < dv; c += 32) out[row * dv + c] = from_f32<TO>(((src[c] * inv) * weight[h * dv + c]) * sigmoidf_(g[c]));
+    for (int c = lane; c < dv; c += 32) {
+        const float gate = gate_act == 1 ? g[c] * sigmoidf_(g[c]) : sigmoidf_(g[c]);
+        out[row * dv + c] = from_f32<TO>(((src[c] * inv) * weight[h * dv + c]) * gate);
+    }
 }
 
 extern "C" int spy_gated_head_norm(const float* o, const float* proj, long long ld, int off_g, const float* weight, void* out, int out_dtype, int tokens,
-                                   int H, int dv, float eps, cudaStream_t stream)
+                                   int H, int dv, float eps, cudaStream_t stream, int gate_act)
 {
+    if (gate_act != 0 && gate_act != 1) SPY_FAIL("gated_head_norm: gate activation %d (0: sigmoid, 1: SiLU)", gate_act);
     if (tokens <= 0) return 0;
     if (H <= 0 || dv <= 0) SPY_FAIL("gated_head_norm: %d heads of %d", H, dv);
     const long long rows = (long long)tokens * H, blocks = (rows + 7) / 8;
     if (blocks > 0x7fffffffLL) SPY_FAIL("gated_head_norm: %lld rows exceed the grid limit", rows);
     SPY_DISPATCH_DTYPE(out_dtype, TO, {
-        spy_launch(gated_head_norm_kernel<TO>, dim3((unsigned)blocks), dim3(256), 0, stream, o, proj, ld, off_g, weight, (TO*)out, rows, H, dv, eps);
+        spy_launch(gated_head_norm_kernel<TO>, dim3((unsigned)blocks), dim3(256), 0, stream, o, proj, ld, off_g, weight, (TO*)out, rows, H, dv, eps, gate_act);
     })
     SPY_CHECK_LAUNCH("gated_head_norm");
     return 0;
 }
 
-// out[t, j] = tanh(proj[t, off + j]) for j < n: the inner activation of a two-step (low-rank) projection.
+// out[t, j] = act(proj[t, off + j]) for j < n: the inner activation of a two-step (low-rank) projection; act 0: tanh, 1: none.
 template <typename TO>
-__global__ void tanh_cols_kernel(const float* __restrict__ proj, long long ld, int off, int n, TO* __restrict__ out, long long total)
+__global__ void tanh_cols_kernel(const float* __restrict__ proj, long long ld, int off, int n, TO* __restrict__ out, long long total, int act)
 {
     pdl_enter();
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (; i < total; i += stride) {
         const long long t = i / n;
-        out[i] = from_f32<TO>(tanhf(proj[t * ld + off + (i - t * n)]));
+        const float x = proj[t * ld + off + (i - t * n)];
+        out[i] = from_f32<TO>(act == 0 ? tanhf(x) : x);
     }
 }
 
-extern "C" int spy_tanh_cols(const float* proj, long long ld, int off, int n, void* out, int out_dtype, int tokens, cudaStream_t stream)
+extern "C" int spy_tanh_cols(const float* proj, long long ld, int off, int n, void* out, int out_dtype, int tokens, cudaStream_t stream, int act)
 {
     if (tokens <= 0 || n <= 0) return 0;
+    if (act != 0 && act != 1) SPY_FAIL("tanh_cols: activation %d (0: tanh, 1: none)", act);
     const long long total = (long long)tokens * n;
     long long blocks = (total + 255) / 256;
     const long long most = (long long)spy_sm_count() * 32;
     if (blocks > most) blocks = most;
     SPY_DISPATCH_DTYPE(out_dtype, TO, {
-        spy_launch(tanh_cols_kernel<TO>, dim3((int)blocks), dim3(256), 0, stream, proj, ld, off, n, (TO*)out, total);
+        spy_launch(tanh_cols_kernel<TO>, dim3((int)blocks), dim3(256), 0, stream, proj, ld, off, n, (TO*)out, total, act);
     })
     SPY_CHECK_LAUNCH("tanh_cols");
     return 0;

@@ -66,3 +66,56 @@ extern "C" int spy_add_bias(void* out, int dtype, const void* bias, int bias_dty
     return 0;
 }
 
+
+// out[i] = act(x[i]) element by element in 32-bit: the activation of a feed-forward without a gate.
+//   0: relu(x)^2    1: gelu with the tanh approximation, 0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3)))    2: silu    3: relu
+template <typename T>
+__global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, long long total, int act)
+{
+    pdl_enter();
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        const float v = to_f32(x[i]);
+        float r;
+        if (act == 0) { const float p = fmaxf(v, 0.f); r = p * p; }
+        else if (act == 1) r = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+        else if (act == 2) r = v / (1.0f + expf(-v));
+        else r = fmaxf(v, 0.f);
+        out[i] = from_f32<T>(r);
+    }
+}
+
+extern "C" int spy_activation(const void* x, void* out, int dtype, long long total, int act, cudaStream_t stream)
+{
+    if (total <= 0) return 0;
+    if (act < 0 || act > 3) SPY_FAIL("activation: unknown code %d", act);
+    long long blocks = (total + 255) / 256;
+    const long long most = (long long)spy_sm_count() * 32;
+    if (blocks > most) blocks = most;
+    SPY_DISPATCH_DTYPE(dtype, T, {
+        spy_launch(activation_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (const T*)x, (T*)out, total, act);
+    })
+    SPY_CHECK_LAUNCH("activation");
+    return 0;
+}
+
+// x[i] *= scale in place (32-bit): a model whose logits carry a multiplier.
+__global__ void scale_kernel(float* __restrict__ x, long long total, float scale)
+{
+    pdl_enter();
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) x[i] *= scale;
+}
+
+extern "C" int spy_scale(float* x, long long total, float scale, cudaStream_t stream)
+{
+    if (total <= 0) return 0;
+    long long blocks = (total + 255) / 256;
+    const long long most = (long long)spy_sm_count() * 32;
+    if (blocks > most) blocks = most;
+    spy_launch(scale_kernel, dim3((int)blocks), dim3(256), 0, stream, x, total, scale);
+    SPY_CHECK_LAUNCH("scale");
+    return 0;
+}

@@ -323,16 +323,16 @@ def attention_generic(q: torch.Tensor, num_heads: int, head_dim: int, out: torch
     _check(positions, "positions", torch.int32, 1)
     _check(seq_of_token, "seq_of_token", torch.int32, 1)
     T = q.shape[0]
-    num_pages, two, nkv, page_size, hd = pages.shape
-    if two != 2 or hd != head_dim:
-        raise KernelError(f"cache pages: expected [pages, 2, nkv, page_size, {head_dim}], found {tuple(pages.shape)}")
+    num_pages, planes, nkv, page_size, hd = pages.shape
+    if planes not in (1, 2) or hd != head_dim:
+        raise KernelError(f"cache pages: expected [pages, 2 (or 1: the values are the keys), nkv, page_size, {head_dim}], found {tuple(pages.shape)}")
     if q.shape[1] < num_heads * head_dim or tuple(out.shape) != (T, num_heads * head_dim):
         raise KernelError(f"attention: q {tuple(q.shape)} / out {tuple(out.shape)} do not fit {num_heads} heads of {head_dim}")
     if positions.shape[0] != T or seq_of_token.shape[0] != T:
         raise KernelError("attention: positions and seq_of_token must have one entry per token")
     _call("attention_generic", "spy_attention_generic", _ptr(q), ctypes.c_longlong(q.shape[1]), _ptr(out), _code(q, "attention queries"),
           _ptr(pages), _code(pages, "cache pages"), _ptr(block_table), block_table.shape[1], page_size, num_pages, num_heads, nkv, head_dim,
-          _ptr(positions), _ptr(seq_of_token), T, int(window or 0), ctypes.c_float(scale), _ptr(status), _stream())
+          _ptr(positions), _ptr(seq_of_token), T, int(window or 0), ctypes.c_float(scale), _ptr(status), _stream(), planes)
     return out
 
 
@@ -473,8 +473,33 @@ def delta_scan(proj: torch.Tensor, offsets, decay_pre: torch.Tensor, bias_a: tor
     return out
 
 
-def gated_head_norm(o: torch.Tensor, proj: torch.Tensor, gate_offset: int, weight: torch.Tensor, out: torch.Tensor, heads: int, dv: int, eps: float) -> torch.Tensor:
-    """``out = o / rms(o per head) * weight * sigmoid(proj[:, gate_offset : gate_offset + heads * dv])``; ``o`` float32 ``[T, heads * dv]``."""
+def gla_scan(proj: torch.Tensor, offsets, decay_pre: torch.Tensor, decay_bias: torch.Tensor, tau: float, state: torch.Tensor, q_start: torch.Tensor,
+             state_slot: torch.Tensor, num_seqs: int, out: torch.Tensor, heads: int, dk: int, dv: int, q_scale: float,
+             status: Optional[torch.Tensor] = None, longest: Optional[int] = None) -> torch.Tensor:
+    """Gated linear attention with a decay per key channel over every request's tokens of this step, from and into
+    ``state [slots, heads * dk * dv]``: ``S = diag(a) S + k v^T``, ``o = S^T (q_scale q)``, ``a = sigmoid(z + bias)^(1 / tau)``.
+    ``proj [T, ld]`` float32 holds q, k, v at ``offsets = (q, k, v)``; ``decay_pre [T, heads * dk]`` is ``z``."""
+    _scan_common(proj, state, q_start, state_slot, out, heads, dv)
+    if state.dim() != 2 or state.shape[1] != heads * dk * dv:
+        raise KernelError(f"gated linear attention: state {tuple(state.shape)} does not fit {heads} heads of {dk} x {dv}")
+    _check(decay_pre, "decay pre-activation", torch.float32, 2)
+    _check(decay_bias, "decay bias", torch.float32, 1)
+    oq, ok, ov = (int(o) for o in offsets)
+    n = heads * dk
+    if max(oq + n, ok + n, ov + heads * dv) > proj.shape[1] or tuple(decay_pre.shape) != (proj.shape[0], n) or decay_bias.shape[0] != n or not tau > 0:
+        raise KernelError("gated linear attention: the column offsets, the decay or its bias do not fit the projection, or tau is not positive")
+    _call("recurrence", "spy_gla_scan", _ptr(proj), ctypes.c_longlong(proj.shape[1]), oq, ok, ov, _ptr(decay_pre), _ptr(decay_bias), ctypes.c_float(1.0 / tau),
+          _ptr(state), state.shape[0], _ptr(q_start), _ptr(state_slot), int(num_seqs), int(longest or proj.shape[0]), _ptr(out), heads, dk, dv,
+          ctypes.c_float(q_scale), _ptr(status), _stream())
+    return out
+
+
+def gated_head_norm(o: torch.Tensor, proj: torch.Tensor, gate_offset: int, weight: torch.Tensor, out: torch.Tensor, heads: int, dv: int, eps: float,
+                    gate: str = "sigmoid") -> torch.Tensor:
+    """``out = o / rms(o per head) * weight * gate(proj[:, gate_offset : gate_offset + heads * dv])``; ``o`` float32 ``[T, heads * dv]``;
+    ``gate``: ``"sigmoid"`` or ``"silu"``."""
+    if gate not in ("sigmoid", "silu"):
+        raise KernelError(f"gated_head_norm: unknown gate {gate!r}")
     _check(o, "recurrence output", torch.float32, 2)
     _check(proj, "fused projection", torch.float32, 2)
     _check(weight, "head norm weight", torch.float32, 1)
@@ -483,18 +508,21 @@ def gated_head_norm(o: torch.Tensor, proj: torch.Tensor, gate_offset: int, weigh
     if o.shape[1] != n or tuple(out.shape) != tuple(o.shape) or weight.shape[0] != n or gate_offset + n > proj.shape[1] or proj.shape[0] != o.shape[0]:
         raise KernelError("gated_head_norm: shapes do not fit")
     _call("recurrence", "spy_gated_head_norm", _ptr(o), _ptr(proj), ctypes.c_longlong(proj.shape[1]), int(gate_offset), _ptr(weight), _ptr(out),
-          _code(out, "gated output"), o.shape[0], heads, dv, ctypes.c_float(eps), _stream())
+          _code(out, "gated output"), o.shape[0], heads, dv, ctypes.c_float(eps), _stream(), ("sigmoid", "silu").index(gate))
     return out
 
 
-def tanh_cols(proj: torch.Tensor, offset: int, n: int, out: torch.Tensor) -> torch.Tensor:
-    """``out[t, j] = tanh(proj[t, offset + j])`` for ``j < n``; proj float32."""
+def tanh_cols(proj: torch.Tensor, offset: int, n: int, out: torch.Tensor, activation: str = "tanh") -> torch.Tensor:
+    """``out[t, j] = tanh(proj[t, offset + j])`` for ``j < n``; proj float32.  ``activation="none"``: the columns as they are
+    (in ``out``'s type)."""
+    if activation not in ("tanh", "none"):
+        raise KernelError(f"tanh_cols: unknown activation {activation!r}")
     _check(proj, "fused projection", torch.float32, 2)
     _check(out, "tanh output", ndim=2)
     if offset + n > proj.shape[1] or tuple(out.shape) != (proj.shape[0], n):
         raise KernelError("tanh_cols: shapes do not fit")
     _call("recurrence", "spy_tanh_cols", _ptr(proj), ctypes.c_longlong(proj.shape[1]), int(offset), int(n), _ptr(out), _code(out, "tanh output"),
-          proj.shape[0], _stream())
+          proj.shape[0], _stream(), ("tanh", "none").index(activation))
     return out
 
 
@@ -570,9 +598,9 @@ def attention_tc(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tens
     _check(positions, "positions", torch.int32, 1)
     _check(q_start, "q_start", torch.int32, 1)
     T = q.shape[0]
-    num_pages, two, nkv, page_size, hd = pages.shape
-    if two != 2 or hd != head_dim:
-        raise KernelError(f"cache pages: expected [pages, 2, nkv, page_size, {head_dim}], found {tuple(pages.shape)}")
+    num_pages, planes, nkv, page_size, hd = pages.shape
+    if planes not in (1, 2) or hd != head_dim:
+        raise KernelError(f"cache pages: expected [pages, 2 (or 1: the values are the keys), nkv, page_size, {head_dim}], found {tuple(pages.shape)}")
     if q.shape[1] < num_heads * head_dim or tuple(out.shape) != (T, num_heads * head_dim):
         raise KernelError(f"attention: q {tuple(q.shape)} / out {tuple(out.shape)} do not fit {num_heads} heads of {head_dim}")
     if positions.shape[0] != T or q_start.shape[0] != num_seqs + 1 or block_table.shape[0] < num_seqs:
@@ -585,11 +613,11 @@ def attention_tc(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tens
             raise KernelError(f"attention: lse {tuple(lse.shape)} does not fit {T} tokens of {num_heads} heads")
         _call("attention_tc", "spy_attention_tc_lse", _ptr(q), ctypes.c_longlong(q.shape[1]), _ptr(out), _ptr(lse), _ptr(pages), _ptr(block_table),
               block_table.shape[1], page_size, num_pages, num_heads, nkv, head_dim, _ptr(positions), _ptr(q_start), T, num_seqs,
-              int(window or 0), ctypes.c_float(scale), _ptr(status), _stream())
+              int(window or 0), ctypes.c_float(scale), _ptr(status), _stream(), planes)
         return out
     _call("attention_tc", "spy_attention_tc", _ptr(q), ctypes.c_longlong(q.shape[1]), _ptr(out), _ptr(pages), _ptr(block_table),
           block_table.shape[1], page_size, num_pages, num_heads, nkv, head_dim, _ptr(positions), _ptr(q_start), T, num_seqs,
-          int(window or 0), ctypes.c_float(scale), _ptr(status), _stream())
+          int(window or 0), ctypes.c_float(scale), _ptr(status), _stream(), planes)
     return out
 
 
@@ -636,9 +664,9 @@ def attention_decode(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.
     _check(positions, "positions", torch.int32, 1)
     _check(q_start, "q_start", torch.int32, 1)
     T = q.shape[0]
-    num_pages, two, nkv, page_size, hd = pages.shape
-    if two != 2 or hd != head_dim:
-        raise KernelError(f"cache pages: expected [pages, 2, nkv, page_size, {head_dim}], found {tuple(pages.shape)}")
+    num_pages, planes, nkv, page_size, hd = pages.shape
+    if planes not in (1, 2) or hd != head_dim:
+        raise KernelError(f"cache pages: expected [pages, 2 (or 1: the values are the keys), nkv, page_size, {head_dim}], found {tuple(pages.shape)}")
     if q.shape[1] < num_heads * head_dim or tuple(out.shape) != (T, num_heads * head_dim):
         raise KernelError(f"attention: q {tuple(q.shape)} / out {tuple(out.shape)} do not fit {num_heads} heads of {head_dim}")
     if positions.shape[0] != T or q_start.shape[0] != num_seqs + 1 or block_table.shape[0] < num_seqs or T < num_seqs:
@@ -656,12 +684,12 @@ def attention_decode(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.
         _call("attention_decode", "spy_attention_decode_lse", _ptr(q), ctypes.c_longlong(q.shape[1]), _ptr(out), _ptr(lse), _ptr(pages), _ptr(block_table),
               block_table.shape[1], page_size, num_pages, num_heads, nkv, head_dim, _ptr(positions), _ptr(q_start), T, num_seqs,
               int(window or 0), ctypes.c_float(scale), ("auto", "split", "whole").index(share), _ptr(scratch), ctypes.c_longlong(scratch.numel()),
-              _ptr(status), _stream())
+              _ptr(status), _stream(), planes)
         return out
     _call("attention_decode", "spy_attention_decode", _ptr(q), ctypes.c_longlong(q.shape[1]), _ptr(out), _ptr(pages), _ptr(block_table),
           block_table.shape[1], page_size, num_pages, num_heads, nkv, head_dim, _ptr(positions), _ptr(q_start), T, num_seqs,
           int(window or 0), ctypes.c_float(scale), ("auto", "split", "whole").index(share), _ptr(scratch), ctypes.c_longlong(scratch.numel()),
-          _ptr(status), _stream())
+          _ptr(status), _stream(), planes)
     return out
 
 
@@ -697,6 +725,130 @@ def add_bias(out: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
     if bias.shape[0] != out.shape[1]:
         raise KernelError(f"add_bias: a bias of {bias.shape[0]} does not fit rows of {out.shape[1]}")
     _call("swiglu", "spy_add_bias", _ptr(out), _code(out, "bias target"), _ptr(bias), _code(bias, "bias"), out.shape[0], out.shape[1], _stream())
+    return out
+
+
+_ACTIVATIONS = ("relu2", "gelu_tanh", "silu", "relu")
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:
+    """``out = act(x)`` element by element in 32-bit; ``kind``: ``relu2`` (the square of relu), ``gelu_tanh``, ``silu``, ``relu``."""
+    if kind not in _ACTIVATIONS:
+        raise KernelError(f"activation: unknown kind {kind!r} (known: {', '.join(_ACTIVATIONS)})")
+    _check(x, "activation input")
+    _check(out, "activation output", x.dtype)
+    if out.shape != x.shape:
+        raise KernelError("activation: input and output differ in shape")
+    _call("swiglu", "spy_activation", _ptr(x), _ptr(out), _code(x, "activation input"), ctypes.c_longlong(x.numel()), _ACTIVATIONS.index(kind), _stream())
+    return out
+
+
+def scale_(x: torch.Tensor, scale: float) -> torch.Tensor:
+    """``x *= scale`` in place; x float32."""
+    _check(x, "scaled tensor", torch.float32)
+    _call("swiglu", "spy_scale", _ptr(x), ctypes.c_longlong(x.numel()), ctypes.c_float(scale), _stream())
+    return x
+
+
+def residual_norm(hidden: torch.Tensor, y: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float, weight_offset: float = 0.0,
+                  copy: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """``hidden += rms_norm(y) * (weight_offset + weight)`` row by row in 32-bit (``hidden`` float32, in place); ``y`` has hidden's
+    shape or is a stack ``[splits, rows, len]`` of partial sums that are added in order.  ``copy`` (optional, any dtype) receives
+    the new ``hidden``.  With ``y`` None only the copy is made."""
+    _check(hidden, "residual stream", torch.float32, 2)
+    rows, H = hidden.shape
+    yp, splits, stride = _stack_of(y, hidden, "residual_norm input")
+    if y is not None:
+        _check(weight, "residual_norm weight", ndim=1)
+        if weight.shape[0] != H:
+            raise KernelError(f"residual_norm: a weight of {weight.shape[0]} does not fit rows of {H}")
+    if copy is not None:
+        _check(copy, "residual_norm copy", ndim=2)
+        if tuple(copy.shape) != (rows, H):
+            raise KernelError(f"residual_norm: the copy {tuple(copy.shape)} differs from the stream {tuple(hidden.shape)}")
+    _call("residual_norm", "spy_residual_norm", _ptr(hidden), _ptr(yp), _code(yp, "residual_norm input") if yp is not None else 0, splits,
+          ctypes.c_longlong(stride if splits > 1 else 0), _ptr(weight if y is not None else None), _code(weight, "residual_norm weight") if y is not None else 0,
+          ctypes.c_float(weight_offset), _ptr(copy), _code(copy, "residual_norm copy") if copy is not None else 0, rows, H, ctypes.c_float(eps), _stream())
+    return copy
+
+
+def latent_prep(fused: torch.Tensor, q_offset: int, q_rank: int, q_weight: Optional[torch.Tensor], cq_out: Optional[torch.Tensor], c_offset: int, kv_rank: int,
+                c_weight: Optional[torch.Tensor], rot_dim: int, rope_table: Optional[torch.Tensor], interleaved: bool, positions: torch.Tensor,
+                seq_of_token: torch.Tensor, block_table: Optional[torch.Tensor], pages: Optional[torch.Tensor], eps: float,
+                status: Optional[torch.Tensor] = None) -> None:
+    """The norms and the cache store of attention through a latent.  ``fused [T, ld]`` float32 holds, from column ``q_offset``,
+    the query latent (``q_rank`` columns; RMS-normed with ``q_weight`` into ``cq_out [T, q_rank]``) and, from ``c_offset``
+    (negative: nothing is stored), the key/value latent (``kv_rank`` columns, RMS-normed with ``c_weight``) followed by the
+    shared key part (``rot_dim`` columns, rotated by ``rope_table [positions, r, 2]``: pairs ``(j, j + r)`` or, ``interleaved``,
+    ``(2j, 2j + 1)``).  The row ``[latent | rotated part]`` goes to plane 0 of ``pages [num_pages, planes, 1, page_size,
+    kv_rank + rot_dim]`` through ``block_table``."""
+    _check(fused, "fused projection", torch.float32, 2)
+    T, ld = fused.shape
+    _check(positions, "positions", torch.int32, 1)
+    _check(seq_of_token, "seq_of_token", torch.int32, 1)
+    if positions.shape[0] != T or seq_of_token.shape[0] != T:
+        raise KernelError("latent_prep: positions and seq_of_token must have one entry per token")
+    out_code = 0
+    if q_rank > 0:
+        _check(q_weight, "query latent norm weight", torch.float32, 1)
+        _check(cq_out, "query latent", ndim=2)
+        if q_offset < 0 or q_offset + q_rank > ld or q_weight.shape[0] != q_rank or tuple(cq_out.shape) != (T, q_rank):
+            raise KernelError("latent_prep: the query latent's columns, weight or output do not fit")
+        out_code = _code(cq_out, "query latent")
+    rot_half = table_rows = page_size = num_pages = planes = width = cache_code = 0
+    if c_offset >= 0:
+        _check(c_weight, "latent norm weight", torch.float32, 1)
+        _check(pages, "cache pages", ndim=5)
+        _check(block_table, "block table", torch.int32, 2)
+        num_pages, planes, nkv, page_size, hd = pages.shape
+        if planes not in (1, 2) or nkv != 1 or hd != kv_rank + rot_dim or c_offset + hd > ld or c_weight.shape[0] != kv_rank:
+            raise KernelError(f"latent_prep: cache pages {tuple(pages.shape)} do not fit one head of {kv_rank} + {rot_dim}, or the columns do not fit")
+        width, cache_code = block_table.shape[1], _code(pages, "cache pages")
+        if rope_table is not None:
+            _check(rope_table, "rope table", torch.float32, 3)
+            table_rows, rot_half = rope_table.shape[0], rope_table.shape[1]
+            if 2 * rot_half > rot_dim:
+                raise KernelError(f"latent_prep: {rot_half} rotated pairs do not fit a rotated part of {rot_dim}")
+    _call("latent", "spy_latent_prep", _ptr(fused), ctypes.c_longlong(ld), int(q_offset), int(q_rank), _ptr(q_weight), _ptr(cq_out), out_code, int(c_offset),
+          int(kv_rank), _ptr(c_weight), int(rot_dim), _ptr(rope_table), rot_half, table_rows, int(bool(interleaved)), _ptr(positions), _ptr(seq_of_token),
+          _ptr(block_table if c_offset >= 0 else None), width, _ptr(pages if c_offset >= 0 else None), cache_code, page_size, num_pages, planes,
+          ctypes.c_float(eps), T, _ptr(status), _stream())
+
+
+def head_product(x: torch.Tensor, in_head_stride: int, weight: torch.Tensor, out: torch.Tensor, out_head_stride: int, tail: int = 0,
+                 rope_table: Optional[torch.Tensor] = None, interleaved: bool = False, positions: Optional[torch.Tensor] = None,
+                 gate: Optional[torch.Tensor] = None, gate_offset: int = 0, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[t, h * out_head_stride + n] = sum_k weight[h, k, n] * x[t, h * in_head_stride + k]`` (32-bit sums) for a weight
+    ``[heads, K, N]``; x and out ``[T, >= heads * stride]`` of one dtype.  ``tail`` elements that follow each head's K inputs go,
+    rotated by ``rope_table`` at the token's position (pairs as in ``latent_prep``), to the columns after its N results.
+    ``gate`` (float32 ``[T, ld]``): the results are multiplied by ``sigmoid(gate[t, gate_offset + h * N + n])``."""
+    _check(x, "head_product input", ndim=2)
+    _check(out, "head_product output", x.dtype, 2)
+    _check(weight, "head_product weight", ndim=3)
+    H, K, N = weight.shape
+    T = x.shape[0]
+    if (out.shape[0] != T or in_head_stride < K + tail or out_head_stride < N + tail or (H - 1) * in_head_stride + K + tail > x.shape[1]
+            or (H - 1) * out_head_stride + N + tail > out.shape[1]):
+        raise KernelError(f"head_product: input {tuple(x.shape)}, weight {tuple(weight.shape)}, output {tuple(out.shape)} and the strides do not fit")
+    rot_half = table_rows = 0
+    if tail > 0:
+        _check(positions, "positions", torch.int32, 1)
+        if positions.shape[0] != T:
+            raise KernelError("head_product: positions must have one entry per token")
+        if rope_table is not None:
+            _check(rope_table, "rope table", torch.float32, 3)
+            table_rows, rot_half = rope_table.shape[0], rope_table.shape[1]
+            if 2 * rot_half > tail:
+                raise KernelError(f"head_product: {rot_half} rotated pairs do not fit a tail of {tail}")
+    gate_ld = 0
+    if gate is not None:
+        _check(gate, "gate", torch.float32, 2)
+        gate_ld = gate.shape[1]
+        if gate.shape[0] != T or gate_offset < 0 or gate_offset + H * N > gate_ld:
+            raise KernelError("head_product: the gate's columns do not fit")
+    _call("latent", "spy_head_product", _ptr(x), ctypes.c_longlong(x.shape[1]), int(in_head_stride), K, _ptr(weight), _code(weight, "head_product weight"), N,
+          _ptr(out), ctypes.c_longlong(out.shape[1]), int(out_head_stride), _code(x, "head_product input"), int(tail), _ptr(rope_table), rot_half, table_rows,
+          int(bool(interleaved)), _ptr(positions), _ptr(gate), ctypes.c_longlong(gate_ld), int(gate_offset), T, H, _ptr(status), _stream())
     return out
 
 

@@ -30,6 +30,8 @@ class Attention(Mixer):
     projections have bias tensors ``{q,k,v}_proj.bias`` / ``o_proj.bias``)."""
 
     graph_safe = True
+    #: False: the head size must be a multiple of 4 (the kernel that rotates and stores q, k and v reads quads)
+    any_head_dim = False
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
@@ -37,7 +39,7 @@ class Attention(Mixer):
         self.nh, self.nkv, self.hd = int(params["num_heads"]), int(params["num_kv_heads"]), int(params["head_dim"])
         if self.nh % self.nkv:
             raise ValueError(f"attention: {self.nh} heads do not group over {self.nkv} key/value heads")
-        if self.hd % 4 or self.hd > 512:
+        if (self.hd % 4 and not self.any_head_dim) or self.hd > 512:
             raise ValueError(f"attention: head_dim {self.hd} must be a multiple of 4 and at most 512")
         self.qk_norm_eps = params.get("qk_norm_eps")
         self.window = params.get("window")
@@ -129,6 +131,13 @@ class Attention(Mixer):
                                   store=cache.writes, status=batch.status, q_out=q,
                                   pairing=self.position.pairing if self.position is not None else "half")
         out = torch.empty((x.shape[0], self.nh * self.hd), dtype=x.dtype, device=x.device)
+        self.attend(q, out, batch, cache)
+        return self.o(out, defer=self.defer_output)
+
+    def attend(self, q, out, batch, cache):
+        """The attention itself, ``q [T, >= nh hd]`` over the cache into ``out [T, nh hd]``, on the kernel that the sizes, the
+        page size and the kind of batch call for."""
+        x = q
         decoding = batch.one_token_each         # every request brings one token
         boxes = self.tc and cache.page_size in kernels.ATTENTION_TMA_PAGE_SIZES        # a page is one TMA box
         if (boxes and decoding and batch.num_seqs <= kernels.ATTENTION_DECODE_MAX_SEQS and batch.num_seqs * self.nkv <= kernels.ATTENTION_DECODE_MAX_PAIRS
@@ -161,7 +170,7 @@ class Attention(Mixer):
             # the float32 path, head sizes above 128 or no multiple of 8, more than 16 query heads a key/value head
             kernels.attention_generic(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.seq_of_token,
                                       self.scale, window=self.window, status=batch.status)
-        return self.o(out, defer=self.defer_output)
+        return out
 
 
 @register_part("pooled_window_attention")
@@ -266,3 +275,105 @@ class PooledWindowAttention(Attention):
                                pooled.block_table if self.pool else None, batch.positions, batch.seq_of_token, self.scale, self.window, self.pool,
                                status=batch.status, lse=lse)
         return self.o(out, defer=self.defer_output, out_dtype=self.output_dtype)
+
+
+@register_part("latent_attention")
+class LatentAttention(Attention):
+    """Softmax attention whose keys and values are per-head projections of one small latent per token, which is all the
+    cache keeps beside one rotated key part that the heads share; the queries go through a latent of their own.
+
+    With ``h`` the input: ``c_q = rms_norm(W_dq h)``, ``q = W_uq c_q`` laid out head by head as ``[dim | rot_dim]``;
+    ``W_dkv h = [kv_rank | rot_dim]``, ``c = rms_norm`` of the first part, ``k_r`` the rotated second part; per head
+    ``score = (q_n . U_k c + rot(q_r) . k_r) * scale``, ``o = U_v (sum p c)``; optionally ``o * sigmoid(W_g h)``; then ``W_o``.
+    It is computed in the absorbed form, ``(U_k^T q_n) . c``, so the attention runs over one key/value head of size
+    ``kv_rank + rot_dim`` on a cache of one plane (the value is the key row's first ``kv_rank`` elements) with the kernels
+    of ``attention``; see ``csrc/latent.cu``.
+
+    params: ``hidden_size``, ``num_heads``, ``head_dim`` (the unrotated part), ``rot_dim``, ``v_head_dim``, ``q_rank``,
+    ``kv_rank``, ``eps`` (of the two latent norms), ``scale``, ``window`` (None: every earlier key), ``position`` (a rotary
+    part whose ``rotary_dim`` is at most ``rot_dim``, or None), ``gate`` (default false), ``shares_cache`` (true: the layer
+    has no ``W_dkv`` and reads the cache of the run-order entry that its ``RunEntry.cache_of`` names), ``prefix``.  Tensors:
+    ``dq``, ``dq.norm``, ``uq``, ``dkv``, ``dkv.norm``, ``uk``, ``uv``, ``g``, ``o``."""
+
+    graph_safe = True
+    any_head_dim = True
+
+    def __init__(self, params, ctx):
+        self.d, self.rd, self.vd = int(params["head_dim"]), int(params["rot_dim"]), int(params["v_head_dim"])
+        self.q_rank, self.kv_rank = int(params["q_rank"]), int(params["kv_rank"])
+        if min(self.d, self.vd, self.q_rank, self.kv_rank) <= 0 or self.rd < 0:
+            raise ValueError("latent_attention: sizes must be positive")
+        base = dict(params)
+        base.update(num_kv_heads=1, head_dim=self.kv_rank + self.rd, qk_norm_eps=None)
+        if base.get("scale") is None:
+            base["scale"] = 1.0 / math.sqrt(float(self.d + self.rd))
+        if (self.kv_rank + self.rd) > 512:
+            raise ValueError(f"latent_attention: a latent of {self.kv_rank} with a rotated part of {self.rd} exceeds the attention kernels' 512")
+        super().__init__(base, ctx)
+        self.mma = False                        # that kernel reads keys and values from two planes
+        self.eps = float(params["eps"])
+        self.gated, self.shares_cache = bool(params.get("gate", False)), bool(params.get("shares_cache", False))
+        if self.position is not None and 2 * (self.position.rotary_dim // 2) > self.rd:
+            raise ValueError(f"latent_attention: a rotation of {self.position.rotary_dim} elements exceeds the rotated part of {self.rd}")
+        self.width = self.kv_rank + self.rd      # a cache row, and a head of the absorbed query
+        self.c_offset = self.q_rank
+        self.gate_offset = self.q_rank + (0 if self.shares_cache else self.width)
+        self.fused = self.uq = self.uk = self.uv = self.q_norm_w = self.c_norm_w = None
+
+    def weight_decls(self):
+        p, H, W = self.prefix, self.nh, self.hidden
+        decls = [WeightDecl(p + "dq", (self.q_rank, W)), WeightDecl(p + "dq.norm", (self.q_rank,), init="one_plus_normal"),
+                 WeightDecl(p + "uq", (H * (self.d + self.rd), self.q_rank))]
+        if not self.shares_cache:
+            decls += [WeightDecl(p + "dkv", (self.width, W)), WeightDecl(p + "dkv.norm", (self.kv_rank,), init="one_plus_normal")]
+        decls += [WeightDecl(p + "uk", (H * self.d, self.kv_rank)), WeightDecl(p + "uv", (H * self.vd, self.kv_rank))]
+        if self.gated:
+            decls.append(WeightDecl(p + "g", (H * self.vd, W)))
+        return decls + [WeightDecl(p + "o", (W, H * self.vd))]
+
+    def bind(self, tensors):
+        p, H = self.prefix, self.nh
+        rows = [tensors[p + "dq"]] + ([] if self.shares_cache else [tensors[p + "dkv"]]) + ([tensors[p + "g"]] if self.gated else [])
+        if len({t.dtype for t in rows}) > 1:
+            rows = [t.float() for t in rows]
+        self.fused = Linear(torch.cat(rows, dim=0).contiguous(), self.ctx.dtype)
+        self.uq = Linear(tensors[p + "uq"], self.ctx.dtype)
+        self.o = Linear(tensors[p + "o"], self.ctx.dtype)
+        self.uk = tensors[p + "uk"].reshape(H, self.d, self.kv_rank).contiguous()                      # [head][unrotated element][latent]: as stored
+        self.uv = tensors[p + "uv"].reshape(H, self.vd, self.kv_rank).transpose(1, 2).contiguous()     # [head][latent][value element]
+        self.q_norm_w = tensors[p + "dq.norm"].float().contiguous()
+        if not self.shares_cache:
+            self.c_norm_w = tensors[p + "dkv.norm"].float().contiguous()
+
+    def modules(self):
+        mods = ["latent"] + (["attention_tc", "attention_decode"] if self.tc else []) + ["attention_generic"] + self.fused.modules() + self.uq.modules() + self.o.modules()
+        if self.position is not None:
+            mods += self.position.modules()
+        return mods
+
+    def linears(self):
+        return [self.fused, self.uq, self.o]
+
+    def cache_need(self):
+        return PagedCacheNeed(1, self.width, int(self.window) if self.window is not None else None, planes=1)
+
+    def forward(self, x, batch, cache):
+        if self.rope_table is None and self.position is not None:
+            self.rope_table = self.position.rotation_table()
+        if cache.writes == self.shares_cache:
+            raise ValueError("latent_attention: a layer with a key/value projection of its own owns its cache, one without reads another layer's")
+        T, H = x.shape[0], self.nh
+        interleaved = self.position is not None and self.position.pairing == "interleaved"
+        fused = self.fused(x, out_dtype=torch.float32)
+        cq = torch.empty((T, self.q_rank), dtype=x.dtype, device=x.device)
+        kernels.latent_prep(fused, 0, self.q_rank, self.q_norm_w, cq, self.c_offset if cache.writes else -1, self.kv_rank, self.c_norm_w, self.rd,
+                            self.rope_table, interleaved, batch.positions, batch.seq_of_token, cache.block_table, cache.pages, self.eps, status=batch.status)
+        q = self.uq(cq)
+        q_abs = torch.empty((T, H * self.width), dtype=x.dtype, device=x.device)
+        kernels.head_product(q, self.d + self.rd, self.uk, q_abs, self.width, tail=self.rd, rope_table=self.rope_table, interleaved=interleaved,
+                             positions=batch.positions, status=batch.status)
+        mixed = torch.empty((T, H * self.width), dtype=x.dtype, device=x.device)      # per head: [sum p c | sum p k_r]; the second part is not used
+        self.attend(q_abs, mixed, batch, cache)
+        o = torch.empty((T, H * self.vd), dtype=x.dtype, device=x.device)
+        kernels.head_product(mixed, self.width, self.uv, o, self.vd, gate=fused if self.gated else None, gate_offset=self.gate_offset)
+        return self.o(o, defer=self.defer_output)

@@ -7,6 +7,9 @@ added, and hands its own feed-forward output on in the same way.
 """
 from __future__ import annotations
 
+import torch
+
+from .. import kernels
 from .base import Block
 
 _BLOCKS = {}
@@ -39,6 +42,46 @@ class PreNormBlock(Block):
         a = self.mixer.forward(x, batch, cache)
         x = self.ffn_norm.forward_add(hidden, a)
         return hidden, self.feed_forward.forward(x)
+
+
+@register_block("post_norm")
+class PostNormBlock(Block):
+    """``h += norm1(mixer(h)); h += norm2(ffn(h))``: the sublayers read the residual stream itself and the norm sits on
+    their output only; a layer may do without the feed-forward half.  The norms must offer ``add_normed``.  On the
+    bfloat16 path the products read a copy of the stream in that type, which the kernel that adds a sublayer's normed
+    output also writes (one launch a sublayer); the copy that a block leaves is handed to the next block through the
+    batch's ``extras``."""
+
+    graph_safe = True
+    required = ("mixer_norm", "mixer")
+    optional = ("ffn_norm", "feed_forward")
+
+    def __init__(self, parts, params=None):
+        super().__init__(parts, params)
+        if (self.ffn_norm is None) != (self.feed_forward is None):
+            raise ValueError("block arrangement 'post_norm': the feed-forward and its norm come together or not at all")
+        for norm in (self.mixer_norm, self.ffn_norm):
+            if norm is not None and not hasattr(norm, "add_normed"):
+                raise ValueError(f"block arrangement 'post_norm': the norm {norm.kind!r} cannot add its result to the stream")
+            if norm is not None:
+                norm.adds_to_stream = True
+
+    def forward(self, hidden, delta, batch, cache):
+        if delta is not None:
+            raise ValueError("block arrangement 'post_norm' follows a block that left its residual sum to the next norm; it has none ahead of its mixer")
+        held = batch.extras.get("stream_copy")
+        if held is not None and held[0] is hidden:
+            x = held[1]
+        elif self.mixer_norm.ctx.dtype == hidden.dtype:
+            x = hidden
+        else:
+            x = torch.empty(hidden.shape, dtype=self.mixer_norm.ctx.dtype, device=hidden.device)
+            kernels.residual_norm(hidden, None, None, 0.0, copy=x)
+        x = self.mixer_norm.add_normed(hidden, self.mixer.forward(x, batch, cache))
+        if self.feed_forward is not None:
+            x = self.ffn_norm.add_normed(hidden, self.feed_forward.forward(x))
+        batch.extras["stream_copy"] = (hidden, x)
+        return hidden, None
 
 
 @register_block("pre_norm_scaled")

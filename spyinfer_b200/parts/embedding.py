@@ -66,13 +66,14 @@ class TokenEmbedding(Part):
 class LMHead(Part):
     graph_safe = True
     """params: ``vocab_size``, ``hidden_size``, ``tied``, ``weight`` (full name when untied),
-    ``tied_to`` (full name of the embedding table when tied)."""
+    ``tied_to`` (full name of the embedding table when tied), ``scale`` (default 1: the logits' multiplier)."""
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
         self.vocab, self.hidden, self.tied = int(params["vocab_size"]), int(params["hidden_size"]), bool(params["tied"])
         self.weight_name = params["tied_to"] if self.tied else params["weight"]
         self.ignorable = [params["weight"]] if self.tied else []
+        self.scale = float(params.get("scale", 1.0))
         self.linear = None
 
     def weight_decls(self):
@@ -82,10 +83,11 @@ class LMHead(Part):
         self.linear = Linear(tensors[self.weight_name], self.ctx.dtype)
 
     def modules(self):
-        return self.linear.modules()
+        return self.linear.modules() + (["swiglu"] if self.scale != 1.0 else [])
 
     def linears(self):
         return [self.linear]
 
     def forward(self, x):
-        return self.linear(x, out_dtype=torch.float32)
+        logits = self.linear(x, out_dtype=torch.float32)
+        return kernels.scale_(logits, self.scale) if self.scale != 1.0 else logits

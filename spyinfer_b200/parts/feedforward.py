@@ -17,6 +17,47 @@ from .linear import Linear
 from .registry import register_part
 
 
+@register_part("mlp")
+class MLP(FeedForward):
+    """``down(act(up(x)))`` without a gate, no biases.  params: ``hidden_size``, ``intermediate_size``, ``activation``
+    (``relu2``: the square of relu; ``gelu_tanh``; ``silu``; ``relu``), ``prefix``, ``names`` (the two tensors' names after the
+    prefix: ``up``, ``down``)."""
+
+    graph_safe = True
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.hidden, self.inter = int(params["hidden_size"]), int(params["intermediate_size"])
+        self.activation = params.get("activation", "relu2")
+        if self.activation not in kernels._ACTIVATIONS:
+            raise ValueError(f"mlp: activation {self.activation!r} is not implemented ({', '.join(kernels._ACTIVATIONS)})")
+        self.prefix = params.get("prefix", "")
+        self.names = {"up": "up_proj.weight", "down": "down_proj.weight"}
+        self.names.update(params.get("names") or {})
+        self.up = self.down = None
+
+    def weight_decls(self):
+        p, n = self.prefix, self.names
+        return [WeightDecl(p + n["up"], (self.inter, self.hidden)), WeightDecl(p + n["down"], (self.hidden, self.inter))]
+
+    def bind(self, tensors):
+        p, n = self.prefix, self.names
+        self.up = Linear(tensors[p + n["up"]], self.ctx.dtype)
+        self.down = Linear(tensors[p + n["down"]], self.ctx.dtype)
+        self.up.hint_next = False       # only the activation runs between the two products
+
+    def linears(self):
+        return [self.up, self.down]
+
+    def modules(self):
+        return ["swiglu"] + self.up.modules() + self.down.modules()
+
+    def forward(self, x):
+        a = self.up(x)
+        kernels.activation(a, a, self.activation)
+        return self.down(a, defer=self.defer_output)
+
+
 @register_part("gated_mlp")
 class GatedMLP(FeedForward):
     graph_safe = True

@@ -1,4 +1,5 @@
-"""RMSNorm: ``x * (1 / sqrt(mean(x^2) + eps)) * weight``, statistics in 32-bit, plain weight.
+"""RMSNorm: ``x * (1 / sqrt(mean(x^2) + eps)) * weight``, statistics in 32-bit, plain weight
+(or, with ``weight_offset``, a weight that is stored around zero: ``offset + weight``).
 
 Formula: spymaster2h/spyinfer src/backends/cpu/x64/kernels.cpp:168-180; used before the
 mixer, before the feed-forward and before the head (src/models/qwen3.hpp:127-133, 224-230,
@@ -17,20 +18,37 @@ from .registry import register_part
 @register_part("rms_norm")
 class RMSNorm(Norm):
     graph_safe = True
-    """params: ``size``, ``eps``, ``weight`` (the tensor's relative name)."""
+    """params: ``size``, ``eps``, ``weight`` (the tensor's relative name), ``weight_offset`` (default 0; with 1 the stored
+    tensor is the gain's distance from one and the norm multiplies by ``1 + weight``)."""
 
-    kernel_modules = ("rmsnorm",)
+    #: set by a block arrangement that has this norm on a sublayer's output (``add_normed``): it then runs the kernel
+    #: that adds the normed result to the stream, not the one that norms the stream
+    adds_to_stream = False
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
         self.size, self.eps, self.weight_name = int(params["size"]), float(params["eps"]), params.get("weight", "weight")
+        self.weight_offset = float(params.get("weight_offset", 0.0))
         self.weight = None
 
     def weight_decls(self):
-        return [WeightDecl(self.weight_name, (self.size,), init="one_plus_normal")]
+        return [WeightDecl(self.weight_name, (self.size,), init="normal" if self.weight_offset else "one_plus_normal")]
 
     def bind(self, tensors):
         self.weight = tensors[self.weight_name]
+        if self.weight_offset:
+            self.weight = (self.weight.float() + self.weight_offset).contiguous()     # the gain itself, in 32-bit
+
+    def modules(self):
+        return ["residual_norm"] if self.adds_to_stream else ["rmsnorm"]
+
+    def add_normed(self, residual, y):
+        """``residual += norm(y)`` (32-bit, in place) for a block whose norm sits on a sublayer's output; ``y`` may be a
+        stack of float32 partial products.  Returns what the next sublayer reads: the stream itself when the activations
+        are 32-bit, else a copy of it in their type, made by the same kernel."""
+        copy = None if self.ctx.dtype == torch.float32 else torch.empty(residual.shape, dtype=self.ctx.dtype, device=residual.device)
+        kernels.residual_norm(residual, y, self.weight, self.eps, copy=copy)
+        return residual if copy is None else copy
 
     def forward(self, x, out_dtype=None):
         out = torch.empty(x.shape, dtype=out_dtype or self.ctx.dtype, device=x.device)

@@ -9,8 +9,12 @@
 ``w = exp(-exp(-1/2) * sigmoid(W_w2 tanh(W_w1 h) + w0))`` and a removal rate ``a = sigmoid(W_a h + b_a)``; with the unit key
 ``u = k / sqrt(sum k^2 + 1e-6)``: ``S = diag(w) S - (a * u)(u^T S) + k v^T`` (both terms read the old ``S``), ``o = S^T r``.
 
-Both end alike: each head's ``o`` divided by its root mean square, times a weight over all heads, times
-``sigmoid(W_g h)``, then the output projection.  All projections of the input are one fused product with a 32-bit result
+``gated_linear_attention`` (gated linear attention with a decay per key channel): per head ``q, k [dk]``, ``v [dv]`` and the
+decay ``a = sigmoid(W_a2 (W_a1 h) + b)^(1 / tau)``: ``S = diag(a) S + k v^T``, ``o = S^T q``, ``q`` scaled by ``dk^(-1/2)``; its
+gate is ``silu(W_g h)`` and its norm weight has one head's size and is shared by the heads.
+
+All end alike: each head's ``o`` divided by its root mean square, times a weight over all heads, times
+a gate of ``W_g h`` (a sigmoid unless said otherwise), then the output projection.  All projections of the input are one fused product with a 32-bit result
 (what enters the recurrence is never rounded to 16 bits); the state lives in the request's slot of the cache manager.
 """
 from __future__ import annotations
@@ -29,6 +33,7 @@ _TILE = 8     # value columns of the narrowest tile of the scan kernel, each of 
 
 class _Recurrent(Mixer):
     graph_safe = True
+    gate = "sigmoid"       # the output gate's activation
 
     #: (relative tensor name, rows as a function of the sizes) of the projections that are fused, in column order
     def _fused_names(self):
@@ -45,7 +50,7 @@ class _Recurrent(Mixer):
 
     def _finish(self, o, proj, gate_offset, heads, dv):
         y = torch.empty(o.shape, dtype=self.ctx.dtype, device=o.device)
-        kernels.gated_head_norm(o, proj, gate_offset, self.norm_weight, y, heads, dv, self.eps)
+        kernels.gated_head_norm(o, proj, gate_offset, self.norm_weight, y, heads, dv, self.eps, gate=self.gate)
         return self.o(y, defer=self.defer_output, out_dtype=self.output_dtype)
 
 
@@ -146,3 +151,57 @@ class DeltaRule(_Recurrent):
         kernels.delta_scan(proj, self.offsets, decay_pre, self.bias_a, self.decay_offset, cache.state, batch.q_start, batch.state_slot,
                            batch.num_seqs, o, self.heads, self.d, status=batch.status, longest=1 if batch.one_token_each else batch.num_tokens)
         return self._finish(o, proj, self.gate_offset, self.heads, self.d)
+
+
+@register_part("gated_linear_attention")
+class GatedLinearAttention(_Recurrent):
+    """params: ``hidden_size``, ``heads``, ``dim`` (q/k size a head), ``vdim`` (value size a head), ``tau`` (the decay's
+    temperature), ``decay_rank`` (inner size of the decay's two-step projection), ``eps`` (of the per-head norm), ``prefix``.
+    Tensors: ``q, k [heads dim, hidden]``, ``v, g [heads vdim, hidden]``, ``a1 [rank, hidden]``, ``a2 [heads dim, rank]``,
+    ``a2.b [heads dim]``, ``norm [vdim]`` (one head's, shared), ``o [hidden, heads vdim]``."""
+
+    gate = "silu"
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.hidden, self.heads = int(params["hidden_size"]), int(params["heads"])
+        self.dk, self.dv, self.rank = int(params["dim"]), int(params["vdim"]), int(params["decay_rank"])
+        self.tau, self.eps = float(params["tau"]), float(params["eps"])
+        if not self.tau > 0.0 or min(self.hidden, self.heads, self.dk, self.dv, self.rank) <= 0:
+            raise ValueError("gated_linear_attention: sizes and tau must be positive")
+        self.prefix = params.get("prefix", "")
+        H, dk, dv = self.heads, self.dk, self.dv
+        self.offsets = (0, H * dk, 2 * H * dk)                       # q, k, v
+        self.gate_offset, self.rank_offset = 2 * H * dk + H * dv, 2 * H * dk + 2 * H * dv
+        self.fused = self.a2 = self.o = self.norm_weight = self.decay_bias = None
+
+    def weight_decls(self):
+        p, H, dk, dv, W, R = self.prefix, self.heads, self.dk, self.dv, self.hidden, self.rank
+        return [WeightDecl(p + "q", (H * dk, W)), WeightDecl(p + "k", (H * dk, W)), WeightDecl(p + "v", (H * dv, W)), WeightDecl(p + "g", (H * dv, W)),
+                WeightDecl(p + "o", (W, H * dv)), WeightDecl(p + "norm", (dv,), init="one_plus_normal"), WeightDecl(p + "a1", (R, W)),
+                WeightDecl(p + "a2", (H * dk, R)), WeightDecl(p + "a2.b", (H * dk,))]
+
+    def bind(self, tensors):
+        self._bind_common(tensors, ("q", "k", "v", "g", "a1"), "o")
+        self.norm_weight = self.norm_weight.repeat(self.heads).contiguous()      # one head's weight, for every head
+        self.a2 = Linear(tensors[self.prefix + "a2"], self.ctx.dtype)
+        self.decay_bias = tensors[self.prefix + "a2.b"].float().contiguous()
+
+    def modules(self):
+        return ["recurrence"] + self.fused.modules() + self.a2.modules() + self.o.modules()
+
+    def linears(self):
+        return [self.fused, self.a2, self.o]
+
+    def cache_need(self):
+        return StateCacheNeed((self.heads * self.dk * self.dv,), "float32")
+
+    def forward(self, x, batch, cache):
+        proj = self.fused(x, out_dtype=torch.float32)
+        inner = torch.empty((x.shape[0], self.rank), dtype=self.ctx.dtype, device=x.device)
+        kernels.tanh_cols(proj, self.rank_offset, self.rank, inner, activation="none")
+        decay_pre = self.a2(inner, out_dtype=torch.float32)
+        o = torch.empty((x.shape[0], self.heads * self.dv), dtype=torch.float32, device=x.device)
+        kernels.gla_scan(proj, self.offsets, decay_pre, self.decay_bias, self.tau, cache.state, batch.q_start, batch.state_slot, batch.num_seqs, o,
+                         self.heads, self.dk, self.dv, self.dk ** -0.5, status=batch.status, longest=1 if batch.one_token_each else batch.num_tokens)
+        return self._finish(o, proj, self.gate_offset, self.heads, self.dv)
