@@ -117,8 +117,9 @@ class Model:
     # ---- cache needs -------------------------------------------------------------------------
     def cache_needs(self):
         """Per run-order entry: its mixer's need, and the entry whose cache it reads instead."""
-        needs = [self.layers[e.layer].mixer.cache_need() if self.layers[e.layer].mixer is not None else None for e in self.spec.run_order]
         cache_of = [e.cache_of for e in self.spec.run_order]
+        needs = [self.layers[e.layer].mixer.cache_need() if self.layers[e.layer].mixer is not None and e.cache_of is None else None
+                 for e in self.spec.run_order]               # an entry that reads another's cache keeps nothing of its own
         # what the embedding keeps between steps (a request's last token, if it looks at pairs of tokens) comes after the
         # run order's entries, as one more entry of the cache manager
         own = getattr(self.embedding, "cache_need", lambda: None)()
