@@ -3,6 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--shape 8b|14b|32b] [--batch B] [--context C] [--impl ours|reference]
     python bench.py --workload mixed [--shape 14b] [--requests 64] [--budget 2048]     (a continuous batch through LLMEngine; its own line)
+    python bench.py --workload nezolorn | daronex [--layers 6] [--prefill-tokens 2048]   (another design beside Qwen3 at equal layer sizes; its own line)
 
 The model has the layer sizes of Qwen3-8B (36 layers, hidden 4096, 32 query heads, 8 key/value
 heads, head size 128, intermediate 12288, vocabulary 151936, untied head) with seeded random
@@ -362,6 +363,121 @@ def mixed_workload(args, model_config, layers, full_layers, page) -> int:
     return 0
 
 
+def _measure_design(args, cfg_json, vocab, page, T, ctx, annotate):
+    """One model of ``--workload nezolorn`` / ``daronex``: a prompt of ``T`` tokens in one step, decoding at batch 8 and 64 from ``ctx``
+    tokens, and every kernel's time inside one prompt step and one decode step of batch 64 launched one by one;
+    ``annotate(res, rate)`` adds achieved rates (``rate(block, kernel function, flops=, nbytes=)``)."""
+    import torch
+
+    from spyinfer_b200 import config_from_json, kernels
+    from spyinfer_b200.engine import LLMEngine
+    from spyinfer_b200.engine.batch import StepEntry
+
+    hbm_gbs, bf16_tflops, _, _ = peaks()
+    batch_max = 64
+    pages_per_req = (ctx + args.steps + 16 + page - 1) // page + 1
+    num_pages = batch_max * pages_per_req + (T + page - 1) // page + 8
+    engine = LLMEngine(model_config=config_from_json(cfg_json), seed=0, dtype="bfloat16", max_num_seqs=batch_max, max_model_len=max(ctx + args.steps + 16, T) + 16,
+                       kvcache_block_size=page, num_kvcache_blocks=num_pages, max_num_batched_tokens=max(T, batch_max))
+    runner, cache = engine.runner, engine.runner.cache
+    for g in cache.groups:
+        g.pages.normal_(0.0, 1.0)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, vocab, (T,), generator=g).tolist()
+
+    def events():
+        return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def prefill_ms(reps, warm):
+        total = 0.0
+        for i in range(warm + reps):
+            e0, e1 = events()
+            e0.record()
+            runner.step([StepEntry("p", prompt, [T - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            runner.finish("p")
+            if i >= warm:
+                total += e0.elapsed_time(e1)
+        return total / reps
+
+    def fake(batch, context):
+        rids = [f"d{i}" for i in range(batch)]
+        for r in rids:
+            cache.add_request(r)
+            cache.reserve(r, context)
+            cache.commit(r, context)
+        return rids
+
+    def decode_ms(batch, steps, warm):
+        rids = fake(batch, ctx)
+        toks = torch.randint(0, vocab, (steps + warm, batch), generator=g).tolist()
+        e0, e1 = events()
+        for i in range(steps + warm):
+            if i == warm:
+                torch.cuda.synchronize()
+                e0.record()
+            runner.step([StepEntry(r, [toks[i][j]], [0]) for j, r in enumerate(rids)])
+        e1.record()
+        torch.cuda.synchronize()
+        for r in rids:
+            runner.finish(r)
+        return e0.elapsed_time(e1) / steps
+
+    def kernel_times(run):
+        """Microseconds of every kernel function inside one step launched one by one (no graph)."""
+        graphs, runner._use_graphs = runner._use_graphs, False
+        try:
+            run()                                  # warm: lazy allocations, first launches
+            sink = []
+            kernels.time_calls(sink)
+            run()
+            kernels.time_calls(None)
+            torch.cuda.synchronize()
+        finally:
+            kernels.time_calls(None)
+            runner._use_graphs = graphs
+        out = {}
+        for fn, a, b in sink:
+            us, n = out.get(fn, (0.0, 0))
+            out[fn] = (us + a.elapsed_time(b) * 1e3, n + 1)
+        return {fn: {"us": round(us, 1), "launches": n} for fn, (us, n) in sorted(out.items(), key=lambda kv: -kv[1][0])}
+
+    def prompt_once():
+        runner.step([StepEntry("p", prompt, [T - 1])])
+        torch.cuda.synchronize()
+        runner.finish("p")
+
+    res = {"prefill": {}, "decode": {}}
+    ms = prefill_ms(5, 3)
+    res["prefill"] = {"tokens": T, "ms": round(ms, 3), "tokens_per_s": round(T / ms * 1e3, 1)}
+    for b in (8, 64):
+        ms = decode_ms(b, args.steps, 3)
+        res["decode"][f"b{b}_ctx{ctx}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(b / ms * 1e3, 1)}
+    res["kernels_prefill"] = kernel_times(prompt_once)
+    rids = fake(64, ctx)
+    toks = torch.randint(0, vocab, (64,), generator=g).tolist()
+    res["kernels_decode_b64"] = kernel_times(lambda: runner.step([StepEntry(r, [toks[j]], [0]) for j, r in enumerate(rids)]))
+    for r in rids:
+        runner.finish(r)
+
+    def rate(block, fn, flops=None, nbytes=None):
+        k = res[block].get(fn)
+        if not k or k["us"] <= 0:
+            return
+        if flops is not None:
+            k["tflops"] = round(flops / k["us"] * 1e-6, 1)
+            k["frac_of_bf16_peak"] = round(flops / k["us"] * 1e-6 / bf16_tflops, 4)
+        if nbytes is not None:
+            k["gbs"] = round(nbytes / k["us"] * 1e-3, 1)
+            k["frac_of_copy_rate"] = round(nbytes / k["us"] * 1e-3 / hbm_gbs, 4)
+
+    annotate(res, rate)
+    del engine, runner, cache
+    torch.cuda.empty_cache()
+    return res
+
+
 def nezolorn_workload(args) -> int:
     """``--workload nezolorn``: prefill and decode throughput of the Nezolorn design (layers of pooled-window attention
     beside a gated matrix memory, and delta-rule layers) at two layer sizes that resemble real models, beside the
@@ -398,125 +514,28 @@ def nezolorn_workload(args) -> int:
         return {"nezolorn": nz, "qwen3": qw}
 
     def measure(cfg_json, z, name):
-        batch_max = 64
-        pages_per_req = (ctx + args.steps + 16 + page - 1) // page + 1
-        num_pages = batch_max * pages_per_req + (T + page - 1) // page + 8
-        engine = LLMEngine(model_config=config_from_json(cfg_json), seed=0, dtype="bfloat16", max_num_seqs=batch_max, max_model_len=max(ctx + args.steps + 16, T) + 16,
-                           kvcache_block_size=page, num_kvcache_blocks=num_pages, max_num_batched_tokens=max(T, batch_max))
-        runner, cache = engine.runner, engine.runner.cache
-        for g in cache.groups:
-            g.pages.normal_(0.0, 1.0)
-        g = torch.Generator().manual_seed(1)
-        prompt = torch.randint(0, vocab, (T,), generator=g).tolist()
+        def annotate(res, rate):
+            nh, nkv, hd = z["heads"], z["kv"], z["hd"]
+            n_att = sum(1 for i in range(layers) if i % 3 != 2) if name == "nezolorn" else layers
 
-        def events():
-            return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if name == "nezolorn":
+                keys = sum(min(window, p + 1) for p in range(T))
+                rate("kernels_prefill", "attention_tc.spy_attention_tc_lse", flops=4.0 * keys * nh * hd * n_att)
+                rate("kernels_decode_b64", "attention_decode.spy_attention_decode_lse", nbytes=64.0 * nkv * min(window, ctx + 1) * hd * 2 * 2 * n_att)
+                n_mem, n_delta = n_att, layers - n_att
+                mem_state = nkv * kernels.mlstm_record(hd, 2 * hd) * 4
+                rate("kernels_decode_b64", "recurrence.spy_mlstm_scan", nbytes=64.0 * 2 * mem_state * n_mem)
+                rate("kernels_decode_b64", "recurrence.spy_delta_scan", nbytes=64.0 * 2 * (z["width"] // 128) * 64 * 64 * 4 * n_delta)
+                norm_fn, norms = "layernorm.spy_layernorm", 2 * layers
+            else:
+                rate("kernels_prefill", "attention_tc.spy_attention_tc", flops=4.0 * (T * (T + 1) / 2) * nh * hd * n_att)
+                rate("kernels_decode_b64", "attention_decode.spy_attention_decode", nbytes=64.0 * nkv * (ctx + 1) * hd * 2 * 2 * n_att)
+                norm_fn, norms = "rmsnorm.spy_rmsnorm", 2 * layers
+            # a norm with the residual sum: reads the stream and the delta (32-bit), writes the stream and a bfloat16 row
+            rate("kernels_prefill", norm_fn, nbytes=float(norms) * T * z["width"] * (4 + 4 + 4 + 2))
 
-        def prefill_ms(reps, warm):
-            total = 0.0
-            for i in range(warm + reps):
-                e0, e1 = events()
-                e0.record()
-                runner.step([StepEntry("p", prompt, [T - 1])])
-                e1.record()
-                torch.cuda.synchronize()
-                runner.finish("p")
-                if i >= warm:
-                    total += e0.elapsed_time(e1)
-            return total / reps
 
-        def fake(batch, context):
-            rids = [f"d{i}" for i in range(batch)]
-            for r in rids:
-                cache.add_request(r)
-                cache.reserve(r, context)
-                cache.commit(r, context)
-            return rids
-
-        def decode_ms(batch, steps, warm):
-            rids = fake(batch, ctx)
-            toks = torch.randint(0, vocab, (steps + warm, batch), generator=g).tolist()
-            e0, e1 = events()
-            for i in range(steps + warm):
-                if i == warm:
-                    torch.cuda.synchronize()
-                    e0.record()
-                runner.step([StepEntry(r, [toks[i][j]], [0]) for j, r in enumerate(rids)])
-            e1.record()
-            torch.cuda.synchronize()
-            for r in rids:
-                runner.finish(r)
-            return e0.elapsed_time(e1) / steps
-
-        def kernel_times(run):
-            """Microseconds of every kernel function inside one step launched one by one (no graph)."""
-            graphs, runner._use_graphs = runner._use_graphs, False
-            try:
-                run()                                  # warm: lazy allocations, first launches
-                sink = []
-                kernels.time_calls(sink)
-                run()
-                kernels.time_calls(None)
-                torch.cuda.synchronize()
-            finally:
-                kernels.time_calls(None)
-                runner._use_graphs = graphs
-            out = {}
-            for fn, a, b in sink:
-                us, n = out.get(fn, (0.0, 0))
-                out[fn] = (us + a.elapsed_time(b) * 1e3, n + 1)
-            return {fn: {"us": round(us, 1), "launches": n} for fn, (us, n) in sorted(out.items(), key=lambda kv: -kv[1][0])}
-
-        def prompt_once():
-            runner.step([StepEntry("p", prompt, [T - 1])])
-            torch.cuda.synchronize()
-            runner.finish("p")
-
-        res = {"prefill": {}, "decode": {}}
-        ms = prefill_ms(5, 3)
-        res["prefill"] = {"tokens": T, "ms": round(ms, 3), "tokens_per_s": round(T / ms * 1e3, 1)}
-        for b in (8, 64):
-            ms = decode_ms(b, args.steps, 3)
-            res["decode"][f"b{b}_ctx{ctx}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(b / ms * 1e3, 1)}
-        res["kernels_prefill"] = kernel_times(prompt_once)
-        rids = fake(64, ctx)
-        toks = torch.randint(0, vocab, (64,), generator=g).tolist()
-        res["kernels_decode_b64"] = kernel_times(lambda: runner.step([StepEntry(r, [toks[j]], [0]) for j, r in enumerate(rids)]))
-        for r in rids:
-            runner.finish(r)
-        # the achieved rates of the kernels that have a like kernel in the other model
-        nh, nkv, hd = z["heads"], z["kv"], z["hd"]
-        n_att = sum(1 for i in range(layers) if i % 3 != 2) if name == "nezolorn" else layers
-
-        def rate(block, fn, flops=None, nbytes=None):
-            k = res[block].get(fn)
-            if not k or k["us"] <= 0:
-                return
-            if flops is not None:
-                k["tflops"] = round(flops / k["us"] * 1e-6, 1)
-                k["frac_of_bf16_peak"] = round(flops / k["us"] * 1e-6 / bf16_tflops, 4)
-            if nbytes is not None:
-                k["gbs"] = round(nbytes / k["us"] * 1e-3, 1)
-                k["frac_of_copy_rate"] = round(nbytes / k["us"] * 1e-3 / hbm_gbs, 4)
-
-        if name == "nezolorn":
-            keys = sum(min(window, p + 1) for p in range(T))
-            rate("kernels_prefill", "attention_tc.spy_attention_tc_lse", flops=4.0 * keys * nh * hd * n_att)
-            rate("kernels_decode_b64", "attention_decode.spy_attention_decode_lse", nbytes=64.0 * nkv * min(window, ctx + 1) * hd * 2 * 2 * n_att)
-            n_mem, n_delta = n_att, layers - n_att
-            mem_state = nkv * kernels.mlstm_record(hd, 2 * hd) * 4
-            rate("kernels_decode_b64", "recurrence.spy_mlstm_scan", nbytes=64.0 * 2 * mem_state * n_mem)
-            rate("kernels_decode_b64", "recurrence.spy_delta_scan", nbytes=64.0 * 2 * (z["width"] // 128) * 64 * 64 * 4 * n_delta)
-            norm_fn, norms = "layernorm.spy_layernorm", 2 * layers
-        else:
-            rate("kernels_prefill", "attention_tc.spy_attention_tc", flops=4.0 * (T * (T + 1) / 2) * nh * hd * n_att)
-            rate("kernels_decode_b64", "attention_decode.spy_attention_decode", nbytes=64.0 * nkv * (ctx + 1) * hd * 2 * 2 * n_att)
-            norm_fn, norms = "rmsnorm.spy_rmsnorm", 2 * layers
-        # a norm with the residual sum: reads the stream and the delta (32-bit), writes the stream and a bfloat16 row
-        rate("kernels_prefill", norm_fn, nbytes=float(norms) * T * z["width"] * (4 + 4 + 4 + 2))
-        del engine, runner, cache
-        torch.cuda.empty_cache()
-        return res
+        return _measure_design(args, cfg_json, vocab, page, T, ctx, annotate)
 
     out_sizes = {}
     with ClockSampler() as clocks:
@@ -529,6 +548,78 @@ def nezolorn_workload(args) -> int:
                       "data": "synthetic: seeded random weights and random token ids",
                       "config": {"layers": layers, "vocab": vocab, "prefill_tokens": T, "decode_context": ctx, "window": window, "pool": pool, "page_size": page,
                                  "pattern": "two layers of pooled-window attention beside a matrix memory, then one delta-rule layer",
+                                 "timing": "CUDA events; inputs (weights, caches and states of 64 requests) exceed L2"},
+                      "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops, "source": peak_src}, "sizes": out_sizes, "clocks": clocks.summary()}))
+    return 0
+
+
+def daronex_workload(args) -> int:
+    """``--workload daronex``: prefill and decode throughput of the Daronex design (layers of attention through a latent,
+    with every key or a window, and of gated linear attention, the norm on each sublayer's output) at two layer sizes that
+    resemble real models, beside the engine's Qwen3 model with the same width, heads, feed-forward size, vocabulary and
+    number of layers (grouped-query attention with heads of 128), all with seeded random weights in bfloat16.  Measured as
+    ``--workload nezolorn`` is: one prompt of ``--prefill-tokens`` tokens, decoding at batch 8 and 64 from ``--context``
+    tokens through the decode graphs, and each kernel's time inside one prompt step and one decode step of batch 64."""
+    import torch
+
+    hbm_gbs, bf16_tflops, _, peak_src = peaks()
+    layers, vocab, page = args.layers or 6, 32000, 16
+    T, ctx = args.prefill_tokens, min(args.context, 4096)
+    window = 1024
+    # the cache row (kv_rank + rot_dim) is 128 wide and there are 16 heads: what the tensor-core attention kernels take
+    sizes = {"width2048": dict(width=2048, heads=16, kv=4, hd=128, ff=8192, dim=64, rot=32, vdim=64, q_rank=768, kv_rank=96, gla_heads=8),
+             "width4096": dict(width=4096, heads=16, kv=4, hd=128, ff=12288, dim=128, rot=32, vdim=128, q_rank=1536, kv_rank=96, gla_heads=16)}
+
+    def configs(z):
+        def latent(windowed):
+            m = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "q_rank": z["q_rank"], "kv_rank": z["kv_rank"],
+                 "scale": (z["dim"] + z["rot"]) ** -0.5, "rot": {"base": 500000.0, "dims": z["rot"]}}
+            if windowed:
+                m["mask"] = {"size": window}
+            return {"type": "latent_attention_2" if windowed else "latent_attention", "mlp": {"kind": "dense", "ff": z["ff"]}, "mixer": m}
+        gla = {"type": "gla", "mlp": {"kind": "dense", "ff": z["ff"]}, "mixer": {"heads": z["gla_heads"], "dim": 128, "vdim": 256, "tau": 16.0, "decay_rank": 64}}
+        dx = {"architecture": "Daronex", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-6}, "logit_scale": 1.0,
+              "layers": [(latent(False), latent(True), gla)[i % 3] for i in range(layers)]}
+        qw = dict(QWEN3_8B)
+        qw.update({"num_hidden_layers": layers, "hidden_size": z["width"], "num_attention_heads": z["heads"], "num_key_value_heads": z["kv"],
+                   "head_dim": z["hd"], "intermediate_size": z["ff"], "vocab_size": vocab})
+        return {"daronex": dx, "qwen3": qw}
+
+    def measure(cfg_json, z, name):
+        def annotate(res, rate):
+            W, H, row = z["width"], z["heads"], z["kv_rank"] + z["rot"]
+            if name == "daronex":
+                n_full, n_win, n_gla = (sum(1 for i in range(layers) if i % 3 == k) for k in range(3))
+                keys_full, keys_win = T * (T + 1) / 2, sum(min(window, p + 1) for p in range(T))
+                # scores over the whole cache row, values over the latent
+                rate("kernels_prefill", "attention_tc.spy_attention_tc", flops=2.0 * (keys_full * n_full + keys_win * n_win) * H * (row + z["kv_rank"]))
+                rate("kernels_decode_b64", "attention_decode.spy_attention_decode", nbytes=64.0 * ((ctx + 1) * n_full + min(window, ctx + 1) * n_win) * row * 2)
+                rate("kernels_decode_b64", "recurrence.spy_gla_scan", nbytes=64.0 * 2 * z["gla_heads"] * 128 * 256 * 4 * n_gla)
+                # the absorbed query and the value expansion: two per-head products a latent layer
+                hp = 2.0 * T * H * (z["dim"] * z["kv_rank"] + z["kv_rank"] * z["vdim"]) * (n_full + n_win)
+                rate("kernels_prefill", "latent.spy_head_product", flops=hp)
+                rate("kernels_prefill", "gemm_tcgen05.spy_gemm_tcgen05_ex", flops=hp)      # where the per-head products run on the tensor cores, they are among these
+                # the norm on a sublayer's output: reads the result (bfloat16 or 32-bit parts) and the stream, writes the stream and its bfloat16 copy
+                rate("kernels_prefill", "residual_norm.spy_residual_norm", nbytes=float(2 * layers) * T * W * (4 + 4 + 4 + 2))
+                rate("kernels_prefill", "swiglu.spy_activation", nbytes=float(layers) * T * z["ff"] * 4)
+            else:
+                rate("kernels_prefill", "attention_tc.spy_attention_tc", flops=4.0 * (T * (T + 1) / 2) * H * z["hd"] * layers)
+                rate("kernels_decode_b64", "attention_decode.spy_attention_decode", nbytes=64.0 * z["kv"] * (ctx + 1) * z["hd"] * 2 * 2 * layers)
+                rate("kernels_prefill", "rmsnorm.spy_rmsnorm", nbytes=float(2 * layers) * T * W * (4 + 4 + 4 + 2))
+
+        return _measure_design(args, cfg_json, vocab, page, T, ctx, annotate)
+
+    out_sizes = {}
+    with ClockSampler() as clocks:
+        for tag, z in sizes.items():
+            out_sizes[tag] = {"layer_sizes": z, "layers": layers}
+            for name, cfg_json in configs(z).items():
+                out_sizes[tag][name] = measure(cfg_json, z, name)
+    print(json.dumps({"metric": "prefill and decode tokens/s of the Daronex design beside Qwen3 at equal layer sizes (bf16, random weights)",
+                      "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": 3, "dtype": "bf16",
+                      "data": "synthetic: seeded random weights and random token ids",
+                      "config": {"layers": layers, "vocab": vocab, "prefill_tokens": T, "decode_context": ctx, "window": window, "page_size": page,
+                                 "pattern": "attention through a latent over every key, the same over a window, gated linear attention; repeated",
                                  "timing": "CUDA events; inputs (weights, caches and states of 64 requests) exceed L2"},
                       "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops, "source": peak_src}, "sizes": out_sizes, "clocks": clocks.summary()}))
     return 0
@@ -548,9 +639,9 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1/64 and short-context points")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel rooflines")
-    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "nezolorn"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "nezolorn", "daronex"],
                     help="decode: the contract's line (default); mixed: a continuous batch of --requests requests with prompts of 64 to 2,048 "
-                         "tokens and 128 generated tokens each through LLMEngine, its own line; nezolorn: prefill and decode of the Nezolorn design "
+                         "tokens and 128 generated tokens each through LLMEngine, its own line; nezolorn, daronex: prefill and decode of that design "
                          "beside Qwen3 at equal layer sizes, its own line")
     ap.add_argument("--requests", type=int, default=64, help="mixed workload: number of requests")
     ap.add_argument("--budget", type=int, default=2048, help="mixed workload: max_num_batched_tokens")
@@ -569,6 +660,8 @@ def main() -> int:
 
     if args.workload == "nezolorn":
         return nezolorn_workload(args)
+    if args.workload == "daronex":
+        return daronex_workload(args)
     hbm_gbs, bf16_tflops, bf16_sustained, peak_src = peaks()
     cfg_json = dict(QWEN3_8B)
     cfg_json.update(SHAPES[args.shape])

@@ -106,9 +106,12 @@ constexpr int SWIGLU_STAGE_LD = 66;   // bf16 elements between the tokens of a s
 // the rest of a tile's read-out (64 tokens: 4.0 against 1.5 microseconds).  A gate below -87 gives
 // g / inf = -0, the limit.  The 32-bit path has its own SwiGLU kernel with the accurate functions.
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+// the square of relu: the activation of a feed-forward without a gate (EPI == 2)
+__device__ __forceinline__ float relu_squared(float v) { const float p = fmaxf(v, 0.f); return p * p; }
 
 // X: the weights [x_rows, K] in the instruction's M slot; Y: the tokens [y_rows, K] in its N slot;
 // out[y, x] (row stride ld).  splits > 1: out is the float scratch [splits][rows][ld] and TC is float.
+// EPI == 2: the result is relu(x)^2 of the product, element by element, in the plain layout; K is not split.
 // EPI == 1 (SwiGLU): the weight's rows alternate gate, up, gate, up, ...; the kernel stores
 // silu(gate) * up, half as many output columns (ld counts those); one pass over K only.
 template <int BN, typename TC, int EPI>
@@ -269,16 +272,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     // 16 bytes a lane (a quarter of the store requests of 4 bytes a lane and token)
                     float* staged = reinterpret_cast<float*>(tiles);
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) staged[(c + j) * PLAIN_STAGE_LD + quarter * 32 + lane] = __uint_as_float(r[j]);
+                    for (int j = 0; j < 32; ++j) staged[(c + j) * PLAIN_STAGE_LD + quarter * 32 + lane] = EPI == 2 ? relu_squared(__uint_as_float(r[j])) : __uint_as_float(r[j]);
                 } else {
                     if (x < x_rows) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
-                            if (j < cols && y + j < y_rows) store_elem(base + (size_t)(y + j) * ld + x, __uint_as_float(r[j]));
+                            if (j < cols && y + j < y_rows) store_elem(base + (size_t)(y + j) * ld + x, EPI == 2 ? relu_squared(__uint_as_float(r[j])) : __uint_as_float(r[j]));
                     }
                 }
             }
-            if constexpr (EPI == 0 && BN >= 32) {
+            if constexpr (EPI != 1 && BN >= 32) {
                 epilogue_barrier();
                 const float* staged = reinterpret_cast<const float*>(tiles);
                 const int e = quarter * 32 + lane;
@@ -383,6 +386,13 @@ __device__ __forceinline__ void store_chunk_normal(TC* base, long long ld, int x
             for (int j = 0; j < 16; ++j)
                 if (j < valid) store_elem(dst + j, __uint_as_float(o[j]));
         }
+    } else if constexpr (EPI == 2) {
+        uint32_t o[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(relu_squared(__uint_as_float(r[j])));
+        TC* dst = base + (size_t)x * ld + y;
+        const bool aligned = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
+        store_row32<TC>(dst, o, min(32, y_rows - y), aligned);
     } else {
         TC* dst = base + (size_t)x * ld + y;
         const bool aligned = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
@@ -1244,6 +1254,7 @@ extern "C" int spy_gemm_tcgen05_plan(int M, int N, int K, long long scratch_limi
 // A [M, K] and W [N, K] bfloat16, rows lda/ldw elements apart; C [M, N] of c_dtype, rows ldc
 // apart.  scratch: float buffer of at least the plan's size (may be null when it is 0).
 // epilogue 1 (SwiGLU): W's rows alternate gate and up rows, C is [M, N / 2], K is not split.
+// epilogue 2: C = relu(A W^T)^2 element by element, K is not split.
 // defer_reduce: when the plan splits K, the partial products stay in scratch as
 // [splits][M][N] floats for the consumer to sum (C is not written); *splits_used tells.
 // next_weights / next_bytes (may be null / 0; used by products of up to 256 tokens only): memory that a
@@ -1263,7 +1274,8 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     if (lda % 8 != 0 || ldw % 8 != 0) SPY_FAIL("gemm_tcgen05: row strides %lld/%lld must be multiples of 8 elements", lda, ldw);
     if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) SPY_FAIL("gemm_tcgen05: operands must be 16-byte aligned");
     if (c_dtype != SPY_F32 && c_dtype != SPY_BF16) SPY_FAIL("gemm_tcgen05: unknown output dtype code %d", c_dtype);
-    if (epilogue != 0 && epilogue != 1) SPY_FAIL("gemm_tcgen05: unknown epilogue %d", epilogue);
+    if (epilogue < 0 || epilogue > 2) SPY_FAIL("gemm_tcgen05: unknown epilogue %d", epilogue);
+    if (epilogue == 2 && c_dtype != SPY_BF16) SPY_FAIL("gemm_tcgen05: the relu-squared epilogue needs bfloat16 output");
     if (epilogue == 1 && (N % 2 != 0 || c_dtype != SPY_BF16)) SPY_FAIL("gemm_tcgen05: the SwiGLU epilogue needs an even N and bfloat16 output");
     Plan plan = make_plan(M, N, K, epilogue == 0);
     if (plan.splits > 1 && (scratch == nullptr || (long long)plan.splits * M * N > scratch_floats)) plan = make_plan(M, N, K, false);
@@ -1298,6 +1310,7 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<bf16, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<float, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<bf16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
+            SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<bf16, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
             const int sms = spy_sm_count();
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(sms / 2 * 2);
@@ -1344,7 +1357,10 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
                 tail_x = tp.x;
             }
         }
-        if (epilogue == 1)
+        if (epilogue == 2)
+            spy_launch_cluster(gemm_tcgen05_pair_kernel<bf16, 2>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (bf16*)C, ldc,
+                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_p, tail_x, scratch, status);
+        else if (epilogue == 1)
             spy_launch_cluster(gemm_tcgen05_pair_kernel<bf16, 1>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (bf16*)C, ldc,
                                M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_p, tail_x, scratch, status);
         else if (c_dtype == SPY_F32)
@@ -1388,8 +1404,12 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<bf16, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WideTile::SMEM));
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<float, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WideTile::SMEM));
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<bf16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WideTile::SMEM));
+            SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<bf16, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WideTile::SMEM));
         }
-        if (epilogue == 1)
+        if (epilogue == 2)
+            spy_launch(gemm_tcgen05_persistent_kernel<bf16, 2>, dim3(grid), dim3(NUM_THREADS), WideTile::SMEM, stream, mx, my, (bf16*)C, ldc, M, N,
+                       k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status);
+        else if (epilogue == 1)
             spy_launch(gemm_tcgen05_persistent_kernel<bf16, 1>, dim3(grid), dim3(NUM_THREADS), WideTile::SMEM, stream, mx, my, (bf16*)C, ldc, M, N,
                        k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status);
         else if (c_dtype == SPY_F32)
@@ -1404,7 +1424,8 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     if (!swap) SPY_FAIL("gemm_tcgen05: no kernel was chosen for M=%d N=%d K=%d (splits %d)", M, N, K, splits);
     int rc;
 #define SPY_LAUNCH(BN_)                                                                                                             \
-    rc = epilogue == 1 ? launch<BN_, bf16, 1>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes)   \
+    rc = epilogue == 2 ? launch<BN_, bf16, 2>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes)   \
+         : epilogue == 1 ? launch<BN_, bf16, 1>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes)   \
          : f32_out     ? launch<BN_, float, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes)  \
                        : launch<BN_, bf16, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes)
     if (bn == 16) SPY_LAUNCH(16);

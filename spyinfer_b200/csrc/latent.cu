@@ -17,7 +17,7 @@
 SPY_MODULE(spy_latent)
 
 constexpr int PREP_THREADS = 128;
-constexpr int TOK = 8;          // tokens a block of head_product takes (a weight element is loaded once for all of them)
+constexpr int TOK = 8;          // tokens a block of head_product takes (16 for prompts); a weight element is loaded once for all of them
 
 // element j of the rotated vector x[0 .. n) at a position whose table row is cs (cos, sin pairs)
 __device__ __forceinline__ float rotated(const float* x, int j, int rot_half, int interleaved, const float* cs)
@@ -111,32 +111,59 @@ struct HeadProductArgs {
     int* status;
 };
 
-template <typename TA, typename TW>
+constexpr int KC = 32;          // weight rows staged at a time
+constexpr int NC = 128;         // output columns a pass of a block takes: one a thread
+
+// A block takes NT tokens of one head: their inputs wait in shared memory as [input element][token], so that a thread
+// reads four tokens' values at a time, and a weight element is loaded once for all NT tokens.  The weights come through
+// shared memory too, KC rows of the block's 128 columns at a time, every thread's loads of a chunk under way together
+// (a thread that fetched its column's weights one after the other from L2 spent its time waiting for them).  A token's
+// sum runs over the inputs in their order whatever NT is.
+template <typename TA, typename TW, int NT>
 __global__ void __launch_bounds__(128) head_product_kernel(HeadProductArgs A)
 {
-    extern __shared__ float in_s[];        // [TOK][K + tail]
+    extern __shared__ __align__(16) float in_s[];        // [K + tail][NT], then the weights' chunk [KC][NC]
     pdl_enter();
-    const int t0 = blockIdx.x * TOK, h = blockIdx.y, tid = threadIdx.x;
-    const int n_tok = min(TOK, A.T - t0), KT = A.K + A.tail;
+    const int t0 = blockIdx.x * NT, h = blockIdx.y, tid = threadIdx.x;
+    const int n_tok = min(NT, A.T - t0), KT = A.K + A.tail;
+    float* w_s = in_s + (size_t)KT * NT;
     const TA* in = (const TA*)A.in;
     TA* out = (TA*)A.out;
-    for (int idx = tid; idx < TOK * KT; idx += 128) {
+    for (int idx = tid; idx < NT * KT; idx += 128) {
         const int u = idx / KT, k = idx - u * KT;
-        in_s[idx] = u < n_tok ? to_f32(in[(size_t)(t0 + u) * A.in_ld + (size_t)h * A.in_head_stride + k]) : 0.f;
+        in_s[k * NT + u] = u < n_tok ? to_f32(in[(size_t)(t0 + u) * A.in_ld + (size_t)h * A.in_head_stride + k]) : 0.f;
     }
-    __syncthreads();
     const TW* W = (const TW*)A.W + (size_t)h * A.K * A.N;
-    for (int n = tid; n < A.N; n += 128) {
-        float acc[TOK];
+    for (int n0 = 0; n0 < A.N; n0 += NC) {
+        const int n = n0 + tid, cols = min(NC, A.N - n0);
+        float acc[NT];
 #pragma unroll
-        for (int u = 0; u < TOK; ++u) acc[u] = 0.f;
-        for (int k = 0; k < A.K; ++k) {
-            const float w = to_f32(W[(size_t)k * A.N + n]);
+        for (int u = 0; u < NT; ++u) acc[u] = 0.f;
+        for (int k0 = 0; k0 < A.K; k0 += KC) {
+            const int kc = min(KC, A.K - k0);
+            __syncthreads();                             // the chunk before has been used (and, the first time, in_s is written)
+            if (tid < cols) {
+#pragma unroll 8
+                for (int r = 0; r < kc; ++r) w_s[r * NC + tid] = to_f32(W[(size_t)(k0 + r) * A.N + n]);
+            }
+            __syncthreads();
+            if (tid < cols) {
+                for (int r = 0; r < kc; ++r) {
+                    const float w = w_s[r * NC + tid];
 #pragma unroll
-            for (int u = 0; u < TOK; ++u) acc[u] = fmaf(w, in_s[u * KT + k], acc[u]);
+                    for (int u = 0; u < NT; u += 4) {
+                        const float4 x = *reinterpret_cast<const float4*>(in_s + (k0 + r) * NT + u);
+                        acc[u] = fmaf(w, x.x, acc[u]);
+                        acc[u + 1] = fmaf(w, x.y, acc[u + 1]);
+                        acc[u + 2] = fmaf(w, x.z, acc[u + 2]);
+                        acc[u + 3] = fmaf(w, x.w, acc[u + 3]);
+                    }
+                }
+            }
         }
+        if (tid >= cols) continue;
 #pragma unroll
-        for (int u = 0; u < TOK; ++u) {
+        for (int u = 0; u < NT; ++u) {
             if (u < n_tok) {
                 float r = acc[u];
                 if (A.gate != nullptr) {
@@ -156,7 +183,19 @@ __global__ void __launch_bounds__(128) head_product_kernel(HeadProductArgs A)
                 continue;
             }
             const float* cs = A.rope + (size_t)(A.rot_half ? pos : 0) * A.rot_half * 2;
-            out[(size_t)(t0 + u) * A.out_ld + (size_t)h * A.out_head_stride + A.N + j] = from_f32<TA>(rotated(in_s + u * KT + A.K, j, A.rot_half, A.interleaved, cs));
+            // element j of the rotated tail, read from the [element][token] layout
+            float r;
+            if (j >= 2 * A.rot_half) {
+                r = in_s[(A.K + j) * NT + u];
+            } else {
+                int a, first;
+                float x, y;
+                if (A.interleaved) { a = j >> 1; first = (j & 1) == 0; x = in_s[(A.K + 2 * a) * NT + u]; y = in_s[(A.K + 2 * a + 1) * NT + u]; }
+                else { a = j < A.rot_half ? j : j - A.rot_half; first = j < A.rot_half; x = in_s[(A.K + a) * NT + u]; y = in_s[(A.K + a + A.rot_half) * NT + u]; }
+                const float c = cs[2 * a], sn = cs[2 * a + 1];
+                r = first ? x * c - y * sn : y * c + x * sn;
+            }
+            out[(size_t)(t0 + u) * A.out_ld + (size_t)h * A.out_head_stride + A.N + j] = from_f32<TA>(r);
         }
     }
 }
@@ -172,15 +211,16 @@ extern "C" int spy_head_product(const void* in, long long in_ld, int in_head_str
     if (heads <= 0 || heads > 65535 || K <= 0 || N <= 0 || tail < 0) SPY_FAIL("head_product: %d heads, K %d, N %d, tail %d", heads, K, N, tail);
     if (tail > 0 && (positions == nullptr || 2 * rot_half > tail || (rot_half > 0 && rope == nullptr))) SPY_FAIL("head_product: the rotated tail needs positions and a table that fits it");
     if (in_head_stride < K + tail || out_head_stride < N + tail) SPY_FAIL("head_product: a head's columns overlap the next head's");
-    const size_t smem = (size_t)TOK * (K + tail) * sizeof(float);
+    const int nt = tokens >= 1024 ? 16 : TOK;      // prompts: more tokens share a weight element
+    const size_t smem = ((size_t)nt * (K + tail) + (size_t)KC * NC) * sizeof(float);
     if (smem > 160 * 1024) SPY_FAIL("head_product: %d inputs a head do not fit a block's shared memory", K + tail);
     HeadProductArgs A = {in, in_ld, in_head_stride, K, W, N, out, out_ld, out_head_stride, tail, rope, rot_half, table_rows, interleaved, positions,
                          gate, gate_ld, gate_off, tokens, status};
     SPY_DISPATCH_DTYPE(act_dtype, TA, {
         SPY_DISPATCH_DTYPE(w_dtype, TW, {
-            auto kernel = head_product_kernel<TA, TW>;
+            auto kernel = nt == 16 ? head_product_kernel<TA, TW, 16> : head_product_kernel<TA, TW, TOK>;
             if (smem > 48 * 1024) SPY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            spy_launch(kernel, dim3((tokens + TOK - 1) / TOK, heads), dim3(128), smem, stream, A);
+            spy_launch(kernel, dim3((tokens + nt - 1) / nt, heads), dim3(128), smem, stream, A);
         })
     })
     SPY_CHECK_LAUNCH("head_product");

@@ -49,10 +49,16 @@ class MLP(FeedForward):
     def linears(self):
         return [self.up, self.down]
 
+    def _fused(self):
+        # the tensor-core product applies the square of relu in its epilogue: the activation costs no launch and no pass over memory
+        return self.activation == "relu2" and self.up is not None and self.up.fast and self.ctx.dtype == torch.bfloat16
+
     def modules(self):
-        return ["swiglu"] + self.up.modules() + self.down.modules()
+        return ([] if self._fused() else ["swiglu"]) + self.up.modules() + self.down.modules()
 
     def forward(self, x):
+        if self._fused():
+            return self.down(self.up(x, epilogue="relu2"), defer=self.defer_output)
         a = self.up(x)
         kernels.activation(a, a, self.activation)
         return self.down(a, defer=self.defer_output)

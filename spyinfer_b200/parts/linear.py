@@ -51,7 +51,8 @@ class Linear:
 
     def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None, epilogue: Optional[str] = None, defer: bool = False) -> torch.Tensor:
         """``epilogue="swiglu"`` (tensor-core kernel only; the weight's rows must alternate gate
-        and up rows) returns ``silu(gate) * up``.  ``defer=True`` allows the result to come back
+        and up rows) returns ``silu(gate) * up``; ``epilogue="relu2"`` (tensor-core kernel only) the square of relu of the
+        product.  ``defer=True`` allows the result to come back
         as a stack ``[splits, rows, out]`` of float32 partial products that the consumer sums."""
         if self.bias is not None:
             if epilogue is not None:

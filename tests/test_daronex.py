@@ -259,6 +259,25 @@ def test_activations_and_the_logit_multiplier(dtype):
         kernels.activation(x.cuda(), torch.empty_like(x, device="cuda"), "swish2")
 
 
+@gpu
+@pytest.mark.parametrize("M", [1, 8, 40, 100, 128, 200, 300, 640, 1200, 2048])
+@pytest.mark.parametrize("N,K", [(384, 192), (4096, 1024), (6400, 2048)])
+def test_product_with_the_relu_squared_epilogue(M, N, K):
+    """The tensor-core product's epilogue squares relu of the result, on every kernel that the number of tokens selects
+    (few-token tiles of each width, single blocks with shared K blocks, pairs of blocks with a shared last round)."""
+    from spyinfer_b200 import kernels
+
+    g = torch.Generator().manual_seed(M + N)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    out = kernels.gemm_tcgen05(a.cuda(), w.cuda(), epilogue="relu2")
+    want = torch.relu(a.double() @ w.double().T) ** 2
+    assert out.dtype == torch.bfloat16 and tuple(out.shape) == (M, N)
+    assert torch.allclose(out.float().cpu().double(), want, atol=2e-2, rtol=2e-2)
+    with pytest.raises(kernels.KernelError):
+        kernels.gemm_tcgen05(a.cuda(), w.cuda(), epilogue="relu2", out_dtype=torch.float32)
+
+
 def _pages_of(rows, page_size, page_ids, dtype, planes=1):
     """``rows [T, d]`` laid into pages ``[pages, planes, 1, page_size, d]`` (plane 0) at the given page ids, scattered on purpose."""
     T, d = rows.shape
