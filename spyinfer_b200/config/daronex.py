@@ -56,8 +56,8 @@ def _check_latent(kind, m, where, layers, i):
         _int(m, k, where)
     rd = _int(m, "rot_dim", where, least=0)
     _num(m, "scale", where, positive=True)
-    if m["kv_rank"] + rd > 512:
-        raise ConfigError(f"Daronex config.json: {where}: kv_rank + rot_dim = {m['kv_rank'] + rd} exceeds the attention kernels' 512")
+    if m["kv_rank"] + rd > 1024:
+        raise ConfigError(f"Daronex config.json: {where}: kv_rank + rot_dim = {m['kv_rank'] + rd} exceeds the attention kernels' 1024")
     rot = m.get("rot")
     if rd > 0:
         dims = _int(rot, "dims", where + ".rot", least=2)

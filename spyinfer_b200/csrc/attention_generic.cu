@@ -17,6 +17,7 @@
 SPY_MODULE(spy_attention_generic)
 
 constexpr int CHUNK = 128;
+constexpr int ACC = 8;       // output elements a thread owns: head sizes up to ACC * CHUNK
 
 template <typename T> struct Vec4;
 template <> struct Vec4<float> {
@@ -62,7 +63,9 @@ attention_generic_kernel(const TA* __restrict__ q, long long q_row_stride, TA* _
 
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     float m = -INFINITY, l = 0.f;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};  // dims tid, tid+128, tid+256, tid+384
+    float acc[ACC];                       // dims tid, tid + 128, tid + 256, ...
+#pragma unroll
+    for (int r = 0; r < ACC; ++r) acc[r] = 0.f;
     __syncthreads();
 
     for (int c = lo / CHUNK; c <= pos / CHUNK; ++c) {
@@ -109,7 +112,7 @@ attention_generic_kernel(const TA* __restrict__ q, long long q_row_stride, TA* _
         m = m_new;
         const int first = max(lo, c * CHUNK) - c * CHUNK, last = min(pos, c * CHUNK + CHUNK - 1) - c * CHUNK;
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
+        for (int r = 0; r < ACC; ++r) {
             const int d = tid + r * CHUNK;
             if (d < hd) {
                 float a = acc[r] * alpha;
@@ -121,7 +124,7 @@ attention_generic_kernel(const TA* __restrict__ q, long long q_row_stride, TA* _
     }
     TA* o_row = out + ((size_t)t * nh + h) * hd;
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
+    for (int r = 0; r < ACC; ++r) {
         const int d = tid + r * CHUNK;
         if (d < hd) o_row[d] = from_f32<TA>(l > 0.f ? acc[r] / l : 0.f);
     }
@@ -136,7 +139,7 @@ extern "C" int spy_attention_generic(const void* q, long long q_row_stride, void
 {
     if (tokens <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) SPY_FAIL("attention: %d query heads do not group over %d key/value heads", nh, nkv);
-    if (hd <= 0 || hd > 4 * CHUNK) SPY_FAIL("attention: head_dim %d must be positive and at most %d", hd, 4 * CHUNK);
+    if (hd <= 0 || hd > ACC * CHUNK) SPY_FAIL("attention: head_dim %d must be positive and at most %d", hd, ACC * CHUNK);
     if (planes != 1 && planes != 2) SPY_FAIL("attention: a cache of %d planes (1: keys that are the values too, 2: keys and values)", planes);
     if (page_size <= 0 || num_pages <= 0 || table_width <= 0) SPY_FAIL("attention: page_size, num_pages and table_width must be positive");
     if (window < 0) SPY_FAIL("attention: window %d must be 0 (none) or positive", window);

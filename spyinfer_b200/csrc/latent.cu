@@ -122,16 +122,26 @@ constexpr int NC = 128;         // output columns a pass of a block takes: one a
 template <typename TA, typename TW, int NT>
 __global__ void __launch_bounds__(128) head_product_kernel(HeadProductArgs A)
 {
-    extern __shared__ __align__(16) float in_s[];        // [K + tail][NT], then the weights' chunk [KC][NC]
+    extern __shared__ __align__(16) float in_s[];        // [K + tail][NT + 4] (the pad spreads a column's stores over the banks), then the weights' chunk [KC][NC]
+    constexpr int LD = NT + 4;
     pdl_enter();
     const int t0 = blockIdx.x * NT, h = blockIdx.y, tid = threadIdx.x;
     const int n_tok = min(NT, A.T - t0), KT = A.K + A.tail;
-    float* w_s = in_s + (size_t)KT * NT;
+    float* w_s = in_s + (size_t)KT * LD;
     const TA* in = (const TA*)A.in;
     TA* out = (TA*)A.out;
-    for (int idx = tid; idx < NT * KT; idx += 128) {
-        const int u = idx / KT, k = idx - u * KT;
-        in_s[k * NT + u] = u < n_tok ? to_f32(in[(size_t)(t0 + u) * A.in_ld + (size_t)h * A.in_head_stride + k]) : 0.f;
+    for (int first = tid; first < NT * KT; first += 8 * 128) {        // eight loads a thread under way at a time
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int idx = first + j * 128, u = idx / KT, k = idx - u * KT;
+            v[j] = (idx < NT * KT && u < n_tok) ? to_f32(in[(size_t)(t0 + u) * A.in_ld + (size_t)h * A.in_head_stride + k]) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int idx = first + j * 128, u = idx / KT, k = idx - u * KT;
+            if (idx < NT * KT) in_s[k * LD + u] = v[j];
+        }
     }
     const TW* W = (const TW*)A.W + (size_t)h * A.K * A.N;
     for (int n0 = 0; n0 < A.N; n0 += NC) {
@@ -152,7 +162,7 @@ __global__ void __launch_bounds__(128) head_product_kernel(HeadProductArgs A)
                     const float w = w_s[r * NC + tid];
 #pragma unroll
                     for (int u = 0; u < NT; u += 4) {
-                        const float4 x = *reinterpret_cast<const float4*>(in_s + (k0 + r) * NT + u);
+                        const float4 x = *reinterpret_cast<const float4*>(in_s + (k0 + r) * LD + u);
                         acc[u] = fmaf(w, x.x, acc[u]);
                         acc[u + 1] = fmaf(w, x.y, acc[u + 1]);
                         acc[u + 2] = fmaf(w, x.z, acc[u + 2]);
@@ -186,12 +196,12 @@ __global__ void __launch_bounds__(128) head_product_kernel(HeadProductArgs A)
             // element j of the rotated tail, read from the [element][token] layout
             float r;
             if (j >= 2 * A.rot_half) {
-                r = in_s[(A.K + j) * NT + u];
+                r = in_s[(A.K + j) * LD + u];
             } else {
                 int a, first;
                 float x, y;
-                if (A.interleaved) { a = j >> 1; first = (j & 1) == 0; x = in_s[(A.K + 2 * a) * NT + u]; y = in_s[(A.K + 2 * a + 1) * NT + u]; }
-                else { a = j < A.rot_half ? j : j - A.rot_half; first = j < A.rot_half; x = in_s[(A.K + a) * NT + u]; y = in_s[(A.K + a + A.rot_half) * NT + u]; }
+                if (A.interleaved) { a = j >> 1; first = (j & 1) == 0; x = in_s[(A.K + 2 * a) * LD + u]; y = in_s[(A.K + 2 * a + 1) * LD + u]; }
+                else { a = j < A.rot_half ? j : j - A.rot_half; first = j < A.rot_half; x = in_s[(A.K + a) * LD + u]; y = in_s[(A.K + a + A.rot_half) * LD + u]; }
                 const float c = cs[2 * a], sn = cs[2 * a + 1];
                 r = first ? x * c - y * sn : y * c + x * sn;
             }
@@ -211,8 +221,8 @@ extern "C" int spy_head_product(const void* in, long long in_ld, int in_head_str
     if (heads <= 0 || heads > 65535 || K <= 0 || N <= 0 || tail < 0) SPY_FAIL("head_product: %d heads, K %d, N %d, tail %d", heads, K, N, tail);
     if (tail > 0 && (positions == nullptr || 2 * rot_half > tail || (rot_half > 0 && rope == nullptr))) SPY_FAIL("head_product: the rotated tail needs positions and a table that fits it");
     if (in_head_stride < K + tail || out_head_stride < N + tail) SPY_FAIL("head_product: a head's columns overlap the next head's");
-    const int nt = tokens >= 1024 ? 16 : TOK;      // prompts: more tokens share a weight element
-    const size_t smem = ((size_t)nt * (K + tail) + (size_t)KC * NC) * sizeof(float);
+    const int nt = tokens >= 256 ? 16 : TOK;      // prompts: more tokens share a weight element (32 of them cost registers, hence resident blocks, and were slower)
+    const size_t smem = ((size_t)(nt + 4) * (K + tail) + (size_t)KC * NC) * sizeof(float);
     if (smem > 160 * 1024) SPY_FAIL("head_product: %d inputs a head do not fit a block's shared memory", K + tail);
     HeadProductArgs A = {in, in_ld, in_head_stride, K, W, N, out, out_ld, out_head_stride, tail, rope, rot_half, table_rows, interleaved, positions,
                          gate, gate_ld, gate_off, tokens, status};

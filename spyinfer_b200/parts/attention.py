@@ -39,8 +39,8 @@ class Attention(Mixer):
         self.nh, self.nkv, self.hd = int(params["num_heads"]), int(params["num_kv_heads"]), int(params["head_dim"])
         if self.nh % self.nkv:
             raise ValueError(f"attention: {self.nh} heads do not group over {self.nkv} key/value heads")
-        if (self.hd % 4 and not self.any_head_dim) or self.hd > 512:
-            raise ValueError(f"attention: head_dim {self.hd} must be a multiple of 4 and at most 512")
+        if (self.hd % 4 and not self.any_head_dim) or self.hd > 1024:
+            raise ValueError(f"attention: head_dim {self.hd} must be a multiple of 4 and at most 1024")
         self.qk_norm_eps = params.get("qk_norm_eps")
         self.window = params.get("window")
         if self.window is not None and int(self.window) <= 0:
@@ -307,8 +307,8 @@ class LatentAttention(Attention):
         base.update(num_kv_heads=1, head_dim=self.kv_rank + self.rd, qk_norm_eps=None)
         if base.get("scale") is None:
             base["scale"] = 1.0 / math.sqrt(float(self.d + self.rd))
-        if (self.kv_rank + self.rd) > 512:
-            raise ValueError(f"latent_attention: a latent of {self.kv_rank} with a rotated part of {self.rd} exceeds the attention kernels' 512")
+        if (self.kv_rank + self.rd) > 1024:
+            raise ValueError(f"latent_attention: a latent of {self.kv_rank} with a rotated part of {self.rd} exceeds the attention kernels' 1024")
         super().__init__(base, ctx)
         self.mma = False                        # that kernel reads keys and values from two planes
         self.eps = float(params["eps"])
