@@ -55,6 +55,8 @@ def _check_latent(kind, m, where, layers, i):
     for k in ("heads", "dim", "vdim", "q_rank", "kv_rank"):
         _int(m, k, where)
     rd = _int(m, "rot_dim", where, least=0)
+    if m.get("scale") is None:
+        m["scale"] = float(m["dim"] + rd) ** -0.5          # not given: one over the root of a head's query/key size
     _num(m, "scale", where, positive=True)
     if m["kv_rank"] + rd > 1024:
         raise ConfigError(f"Daronex config.json: {where}: kv_rank + rot_dim = {m['kv_rank'] + rd} exceeds the attention kernels' 1024")
@@ -73,7 +75,9 @@ def _check_latent(kind, m, where, layers, i):
         other, om = layers[src], layers[src].get("mixer")
         if other.get("type") != kind or om.get("kv_from") is not None:
             raise ConfigError(f"Daronex config.json: {where}.kv_from names layer {src}, which is no {kind} layer with a key/value projection of its own")
-        if (om.get("kv_rank"), om.get("rot_dim"), om.get("rot"), (om.get("mask") or {}).get("size")) != (m["kv_rank"], rd, rot, (m.get("mask") or {}).get("size")):
+        window = lambda x: (x.get("mask") or {}).get("size") if LATENT_TYPES[kind][1] else None
+        rotation = lambda x: (float(x["rot"]["base"]), int(x["rot"]["dims"])) if x.get("rot_dim") else None
+        if (om.get("kv_rank"), om.get("rot_dim"), rotation(om), window(om)) != (m["kv_rank"], rd, rotation(m), window(m)):
             raise ConfigError(f"Daronex config.json: {where}.kv_from: layer {src}'s kv_rank, rot_dim, rotation or window differ from this layer's")
 
 
