@@ -222,7 +222,7 @@ def test_residual_norm_adds_the_normed_result_and_hands_out_a_copy(dtype):
     from spyinfer_b200 import kernels
 
     g = torch.Generator().manual_seed(3)
-    for rows, n, splits in ((5, 40, 1), (3, 192, 3), (9, 1000, 2)):
+    for rows, n, splits in ((5, 40, 1), (3, 200, 3), (9, 1000, 2), (4, 4096, 5), (2, 6144, 2), (600, 256, 2), (2, 50, 2)):
         h = torch.randn(rows, n, generator=g)
         y = torch.randn(splits, rows, n, generator=g) * 3
         w = (0.1 * torch.randn(n, generator=g)).to(torch.bfloat16)
@@ -261,7 +261,7 @@ def test_activations_and_the_logit_multiplier(dtype):
 
 @gpu
 @pytest.mark.parametrize("M", [1, 8, 40, 100, 128, 200, 300, 640, 1200, 2048])
-@pytest.mark.parametrize("N,K", [(384, 192), (4096, 1024), (6400, 2048)])
+@pytest.mark.parametrize("N,K", [(320, 136), (4096, 1024), (6400, 2048)])
 def test_product_with_the_relu_squared_epilogue(M, N, K):
     """The tensor-core product's epilogue squares relu of the result, on every kernel that the number of tokens selects
     (few-token tiles of each width, single blocks with shared K blocks, pairs of blocks with a shared last round)."""
@@ -290,7 +290,7 @@ def _pages_of(rows, page_size, page_ids, dtype, planes=1):
 @gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("interleaved", [False, True])
-@pytest.mark.parametrize("q_rank,kv_rank,rot_dim,dims,page_size", [(24, 32, 16, 16, 8), (10, 18, 4, 4, 4), (80, 96, 32, 8, 16), (16, 6, 2, 2, 16)])
+@pytest.mark.parametrize("q_rank,kv_rank,rot_dim,dims,page_size", [(24, 32, 16, 16, 8), (10, 18, 4, 4, 4), (72, 96, 32, 8, 16), (16, 6, 2, 2, 16)])
 def test_latent_norms_rotation_and_cache_rows(dtype, interleaved, q_rank, kv_rank, rot_dim, dims, page_size):
     """The query latent's norm, the key/value latent's norm, the rotation of the shared key part and the row's place in
     the pages, for two requests whose tokens are mixed in one batch at positions of their own."""
