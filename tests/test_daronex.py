@@ -362,7 +362,7 @@ def test_per_head_products_with_a_rotated_tail_and_with_a_gate(dtype):
 @gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("window,page_size,heads,rank,rot", [(None, 8, 4, 24, 8), (20, 8, 4, 24, 8), (7, 16, 2, 18, 4), (64, 16, 16, 48, 16), (None, 16, 8, 96, 32),
-                                                              (1, 8, 3, 16, 8)])
+                                                              (1, 8, 3, 16, 8), (40, 16, 2, 512, 64)])
 def test_attention_over_a_cache_of_one_plane_sees_exactly_its_keys(dtype, window, page_size, heads, rank, rot):
     """The cache holds rows ``[latent | rotated part]`` and the values are the rows' first ``rank`` elements.  For many
     (query, target) pairs the query is made to point at one row with a large score: a target far back, at a page's first
@@ -398,7 +398,7 @@ def test_attention_over_a_cache_of_one_plane_sees_exactly_its_keys(dtype, window
     worst = (out.float().cpu().view(T, heads, d)[..., :rank].double() - want).abs().amax(dim=(1, 2))
     assert worst.max().item() < tol, f"query {int(worst.argmax())} differs by {worst.max().item()}"
     if dtype != torch.bfloat16 or not kernels.attention_decode_takes(heads, 1, d, page_size, dtype):
-        assert dtype != torch.bfloat16 or d % 8 != 0 or heads > 16
+        assert dtype != torch.bfloat16 or d % 8 != 0 or heads > 16 or d > 128      # why the tensor-core kernels do not take these sizes
         return
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
     out2 = torch.full((T, heads * d), 3.0, dtype=dtype, device="cuda")                  # one prompt of T tokens ...
